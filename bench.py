@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: RWKV-7 state-passing WKV forward + backward, bf16,
+B=16 T=4096 C=4096 (H=64, N=64, chunk 16), synthetic inputs, on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--op NAME]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+A step = one forward + one backward of the operator over the whole batch.  The batch is
+sharded over the ranks (total work fixed: strong scaling); nothing is exchanged between
+ranks because every (batch, head) unit is independent and this operator has no parameter
+gradient to reduce.  Rank 0 prints ONE JSON line.
+
+  value     tokens/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e       tokens/s through the public operator API from pinned HOST buffers: the step's
+            inputs are copied host->device and all results device->host inside the timed region
+  roofline  dominant kernel (the backward): compulsory HBM bytes / measured kernel time,
+            against the measured copy bandwidth in MEASURED_PEAKS.json
+  cpu_baseline  the reference's PyTorch formula path (oracle port) timed on the host cores on a
+            bounded sample
+`--impl reference` times only that CPU formula path and prints the same line shape.
+`--op` selects one of the other benchmark configurations (wkv4, timex, wkv5, wkv6state).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+
+
+# --------------------------------------------------------------------------------------
+# workloads: name -> description, token count, compulsory bytes (fwd, bwd), runner factory
+# --------------------------------------------------------------------------------------
+class V7Workload:
+    """BASELINE config 5: RWKV-7 state passing, bf16, B16 T4096 C4096 N64 chunk 16."""
+    name = "rwkv7_statepassing_clampw fwd+bwd B16 T4096 C4096 N64 chunk16"
+    B, T, H, N = 16, 4096, 64, 64
+    dtype_name = "bf16"
+    metric = "WKV fwd+bwd tokens/s, RWKV-7 B16 T4096 C4096 bf16"
+
+    def __init__(self, b_local, device, seed_rank):
+        import rwkv_cuda_b200 as R
+        self.R = R
+        B, T, H, N = b_local, self.T, self.H, self.N
+        self.b = B
+        g = torch.Generator(device=device)
+        g.manual_seed(42 + seed_rank)
+        bf = torch.bfloat16
+
+        def mk(scale=1.0):
+            return torch.randn(B, T, H, N, generator=g, device=device) * scale
+
+        # generated on the device for speed, then parked in pinned HOST buffers: the end-to-end
+        # leg starts from those host copies
+        r, k, v = mk(0.5), mk(0.5), mk(0.5)
+        w = mk()
+        kk = torch.nn.functional.normalize(mk(), dim=-1)
+        a, b = -kk, kk * torch.sigmoid(mk())
+        self.host_in = [x.to(bf).cpu().pin_memory() for x in (r, w, k, v, a, b)]
+        self.host_dy = mk().to(bf).cpu().pin_memory()
+        self.host_s0 = (0.1 * torch.randn(B, H, N, N, generator=g, device=device)).cpu().pin_memory()
+        self.host_dsT = torch.randn(B, H, N, N, generator=g, device=device).cpu().pin_memory()
+        del r, k, v, w, kk, a, b
+        dev = device
+        self.dev = dev
+        self.inp = [x.to(dev) for x in self.host_in]
+        self.dy, self.s0, self.dsT = self.host_dy.to(dev), self.host_s0.to(dev), self.host_dsT.to(dev)
+        self.y = torch.empty(B, T, H, N, dtype=bf, device=dev)
+        self.sT = torch.empty(B, H, N, N, device=dev)
+        self.s = torch.empty(B, H, T // 16, N, N, device=dev)
+        self.sa = torch.empty(B, T, H, N, device=dev)
+        self.ds0 = torch.empty(B, H, N, N, device=dev)
+        self.grads = [torch.empty(B, T, H, N, dtype=bf, device=dev) for _ in range(6)]
+        self.host_out = None
+
+    tokens_per_unit_batch = T
+
+    @classmethod
+    def bytes_fwd(cls, B):
+        C = cls.H * cls.N
+        return 14 * C * B * cls.T + 2 * 4 * B * cls.H * cls.N * cls.N
+
+    @classmethod
+    def bytes_bwd(cls, B):
+        C = cls.H * cls.N
+        return 26 * C * B * cls.T + 2 * 4 * B * cls.H * cls.N * cls.N
+
+    def forward(self):
+        self.R.ops.wkv7_forward(self.s0, *self.inp, self.y, self.sT, self.s, self.sa)
+
+    def backward(self):
+        self.R.ops.wkv7_backward(*self.inp, self.dy, self.dsT, self.s, self.sa, self.ds0, *self.grads)
+
+    launches_per_step = 2
+
+    def e2e_step(self):
+        """Host buffers in, host buffers out, through the public operator API."""
+        if self.host_out is None:
+            self.host_out = [torch.empty_like(self.host_in[0]).pin_memory() for _ in range(7)]
+            self.host_sout = [torch.empty_like(self.host_s0).pin_memory() for _ in range(2)]
+        for d, h in zip(self.inp, self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.dy.copy_(self.host_dy, non_blocking=True)
+        self.s0.copy_(self.host_s0, non_blocking=True)
+        self.dsT.copy_(self.host_dsT, non_blocking=True)
+        self.forward()
+        self.backward()
+        for h, d in zip(self.host_out, [self.y] + self.grads):
+            h.copy_(d, non_blocking=True)
+        self.host_sout[0].copy_(self.sT, non_blocking=True)
+        self.host_sout[1].copy_(self.ds0, non_blocking=True)
+
+    def e2e_bytes(self):
+        big = self.host_in[0].numel() * 2
+        st = self.host_s0.numel() * 4
+        return 7 * big + 2 * st, 7 * big + 2 * st
+
+
+def cpu_formula_step(T_cpu, threads):
+    """One fwd+bwd of the reference's RWKV-7 PyTorch formula (oracle port) on the host cores:
+    B=1, T=T_cpu, C=4096, fp32, gradients by autograd, as the reference harness computes them."""
+    from oracle import wkv_oracle as O
+    torch.set_num_threads(threads)
+    H, N = 64, 64
+    C = H * N
+    g = torch.Generator()
+    g.manual_seed(42)
+    mk = lambda s=1.0: (torch.randn(1, T_cpu, C, generator=g) * s).requires_grad_(True)
+    r, k, v, w = mk(0.5), mk(0.5), mk(0.5), mk()
+    kk = torch.nn.functional.normalize(torch.randn(1, T_cpu, H, N, generator=g), dim=-1).view(1, T_cpu, C)
+    a = (-kk).requires_grad_(True)
+    b = (kk * torch.sigmoid(torch.randn(1, T_cpu, C, generator=g))).requires_grad_(True)
+    s0 = (0.1 * torch.randn(1, H, N, N, generator=g)).requires_grad_(True)
+    dy, dsT = torch.randn(1, T_cpu, C, generator=g), torch.randn(1, H, N, N, generator=g)
+    t0 = time.perf_counter()
+    y, sT = O.wkv7(r, w, k, v, a, b, H, s0=s0)
+    torch.autograd.backward([y, sT], [dy, dsT])
+    return time.perf_counter() - t0
+
+
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if bits & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def run_reference_arm(args, rank, world):
+    """CPU arm: the reference's PyTorch formula path (oracle port), all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    T_cpu = 256
+    for _ in range(args.warmup):
+        cpu_formula_step(T_cpu, threads)
+    times = [cpu_formula_step(T_cpu, threads) for _ in range(args.steps)]
+    total = sum(times)
+    val = T_cpu * len(times) / total
+    sample = f"B1 T{T_cpu} C4096 N64 fp32 fwd+bwd per step (autograd through the formula), {threads} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": V7Workload.metric, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": V7Workload.name, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    W = V7Workload
+    assert W.B % world == 0, f"batch {W.B} does not divide over {world} ranks"
+    b_local = W.B // world
+    wl = W(b_local, dev, rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        wl.forward()
+        wl.backward()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream ------------------
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    fe = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(args.steps)]
+    with ClockSampler(local) as clocks:
+        barrier()
+        ev[0].record()
+        for i in range(args.steps):
+            fe[i][0].record()
+            wl.forward()
+            fe[i][1].record()
+            wl.backward()
+            fe[i][2].record()
+        ev[1].record()
+        barrier()
+    ms_total = ev[0].elapsed_time(ev[1])
+    fwd_ms = sum(a.elapsed_time(b) for a, b, _ in fe) / args.steps
+    bwd_ms = sum(b.elapsed_time(c) for _, b, c in fe) / args.steps
+    t = torch.tensor([ms_total, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, fwd_ms, bwd_ms = t.tolist()
+    tokens_step = W.B * W.T
+    value = tokens_step * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end: host buffers through the public API ------------------------------
+    wl.e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        wl.e2e_step()
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_val = tokens_step * args.e2e_steps / (te.item() * 1e-3)
+    h2d, d2h = wl.e2e_bytes()
+
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        bb = W.bytes_bwd(b_local)
+        achieved = bb / (bwd_ms * 1e-3) / 1e9
+        fb = W.bytes_fwd(b_local)
+        out = {
+            "metric": W.metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": W.dtype_name, "data": "synthetic",
+            "config": {"workload": W.name, "global_batch": W.B, "batch_per_gpu": b_local, "seq_len": W.T,
+                       "parallelism": f"batch-sharded x{world}, no collective",
+                       "l2": "inputs (6 x %.0f MB per GPU) exceed the 126 MB L2" % (b_local * W.T * 4096 * 2 / 1e6)},
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            "roofline": {"bound": "hbm", "kernel": "wkv7 backward", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": bb,
+                         "fwd": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak,
+                                 "algorithmic_bytes_per_launch": fb},
+                         "fwd_bwd_frac": (fb + bb) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak},
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": d2h * world, "steps": args.e2e_steps},
+            "gpu_launches": W.launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            T_cpu = 256
+            cpu_formula_step(64, threads)
+            n = 3
+            tt = sum(cpu_formula_step(T_cpu, threads) for _ in range(n))
+            out["cpu_baseline"] = {"value": T_cpu * n / tt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                   "sample": f"{n} x (B1 T{T_cpu} C4096 N64 fp32 fwd+bwd, autograd through the formula)"}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

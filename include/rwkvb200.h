@@ -1,0 +1,176 @@
+/*
+ * rwkvb200 — C ABI of the B200 (sm_100a) WKV / depthwise_conv1d kernels.
+ *
+ * Every entry point replaces one `cuda_forward` / `cuda_backward` host launcher of
+ * BlinkDL/RWKV-CUDA (cited per function, paths inside that project) and is what that
+ * project's pybind / TORCH_LIBRARY bindings would call instead.
+ *
+ * Conventions
+ *   - plain device pointers and sizes only; all tensors contiguous row-major;
+ *   - all buffers are caller-owned; the library keeps no state between calls and
+ *     allocates nothing;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *     kernels are enqueued, not waited for;
+ *   - return value: RWKVB200_OK or a negative RWKVB200_E* code; nothing aborts, nothing
+ *     traps on the device.  rwkvb200_strerror() gives a message for a code and
+ *     rwkvb200_last_error() the detail text of the calling thread's last failure.
+ *   - `dtype` selects the element type of the activation tensors (RWKVB200_F32 or
+ *     RWKVB200_BF16); recurrent state and all accumulation are fp32.
+ *   - head size N = C / H may be any value in 1..128 (the reference bakes it in with -D_N_).
+ */
+#ifndef RWKVB200_H
+#define RWKVB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKVB200_OK 0
+#define RWKVB200_EINVAL (-1)      /* bad size / combination of arguments            */
+#define RWKVB200_ENULL (-2)       /* required pointer is NULL                       */
+#define RWKVB200_EALIGN (-3)      /* pointer not aligned as the kernel needs        */
+#define RWKVB200_EUNSUPPORTED (-4)/* valid request, no kernel instance for it        */
+#define RWKVB200_ECUDA (-5)       /* CUDA runtime reported an error at launch        */
+
+#define RWKVB200_F32 0
+#define RWKVB200_BF16 1
+
+#define RWKVB200_MAX_HEAD_SIZE 128
+
+const char* rwkvb200_strerror(int code);
+const char* rwkvb200_last_error(void);
+/* Library version, and the compute capability the kernels were built for (100). */
+int rwkvb200_version(void);
+int rwkvb200_built_for_sm(void);
+
+/* ---------------------------------------------------------------------------------
+ * RWKV-4 WKV, fp32.  Replaces cuda_forward / cuda_backward of wkv/cuda/wkv_cuda_v2.cu:116-130
+ * (bound in wkv/cuda/wkv_op.cpp:6-11).
+ *   w (C) = -exp(time_decay), u (C); k, v, y, gy, gk, gv (B,T,C).
+ *   gw, gu (B,C): per-batch partial sums, ACCUMULATED into (caller zero-fills, then sums
+ *   over B), gw already multiplied by w as the reference does (wkv_cuda_v2.cu:111-113).
+ *   No limit on T or C (the reference requires T <= 4096).
+ */
+int rwkvb200_wkv4_forward(int B, int T, int C, const float* w, const float* u, const float* k,
+                          const float* v, float* y, void* stream);
+int rwkvb200_wkv4_backward(int B, int T, int C, const float* w, const float* u, const float* k,
+                           const float* v, const float* gy, float* gw, float* gu, float* gk,
+                           float* gv, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * depthwise_conv1d ("TimeX"), fp32.  Replaces cuda_forward / cuda_backward of
+ * depthwise_conv1d/cuda/timex_cuda_v3.cu:140-150 (bound in timex_op.cpp:6-11).
+ *   w (C,T); k, x, gwk, gk (B,C,T); gw (B,C,T) per-batch partials (caller sums over B).
+ *   x[b,c,t] = eps + sum_{u<=t} w[c,(T-1)-(t-u)] k[b,c,u].
+ *   Any B and T (the reference requires T%4==0, T<=Tmax, B%BF==0).
+ * rwkvb200_timex_backward_reduced writes gw already summed over the batch, shape (C,T).
+ */
+int rwkvb200_timex_forward(const float* w, const float* k, float* x, float eps, int B, int C,
+                           int T, void* stream);
+int rwkvb200_timex_backward(const float* w, const float* k, const float* gwk, float* gw,
+                            float* gk, int B, int C, int T, void* stream);
+int rwkvb200_timex_backward_reduced(const float* w, const float* k, const float* gwk,
+                                    float* gw_sum, float* gk, int B, int C, int T, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * RWKV-5 WKV, fp32 or bf16 activations.  Replaces cuda_forward / cuda_backward of
+ * wkv5_bf16/cuda/wkv5_cuda_v1b.cu:179-191 (bf16; wkv5_op.cpp:8-13) and of
+ * wkv5/cuda/wkv5_cuda_v1e.cu (fp32; wkv5/cuda/wkv5_op.cpp:6-11).
+ *   r,k,v,y,gy,gr,gk,gv (B,T,C) and u (H,N) in `dtype`; w = exp(-exp(w_raw)) and
+ *   ww = -exp(w_raw) as fp32 (H,N); gw, gu (B,C) per-batch partials in `dtype`
+ *   (gw already multiplied by ww).
+ */
+int rwkvb200_wkv5_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                          const void* v, const float* w, const void* u, void* y, void* stream);
+int rwkvb200_wkv5_backward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                           const void* v, const float* w, const float* ww, const void* u,
+                           const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * RWKV-5a WKV (decay w1[j]*w2[i], bonus u1[j]+u2[i]), fp32 or bf16 activations.
+ * Replaces cuda_forward / cuda_backward of wkv5a/cuda/wkv5a_cuda_v1a.cu:214-226
+ * (wkv5a_op.cpp:9-17; the reference instantiates DTYPE=float only).
+ */
+int rwkvb200_wkv5a_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                           const void* v, const float* w1, const void* u1, const float* w2,
+                           const void* u2, void* y, void* stream);
+int rwkvb200_wkv5a_backward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                            const void* v, const float* w1, const float* ww1, const void* u1,
+                            const float* w2, const float* ww2, const void* u2, const void* gy,
+                            void* gr, void* gk, void* gv, void* gw1, void* gu1, void* gw2,
+                            void* gu2, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * RWKV-6 WKV (per-token decay), bf16 or fp32 activations.  Replaces cuda_forward /
+ * cuda_backward of wkv6/cuda/wkv6_cuda_v1.cu:211-223 (wkv6_op.cpp:8-13).
+ *   w (B,T,C) fp32 = -exp(w_raw) (the kernel applies exp); gw (B,T,C) in `dtype` w.r.t.
+ *   w_raw; gu (B,C) per-batch partials.
+ *   `scratch`: device buffer of rwkvb200_wkv6_scratch_bytes(B,T,C) bytes used inside the
+ *   backward (contents undefined afterwards).  No limit on T (the reference's backward
+ *   fails for T >= 128, wkv6/run.py:51).
+ */
+size_t rwkvb200_wkv6_scratch_bytes(int B, int T, int C);
+int rwkvb200_wkv6_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                          const void* v, const float* w, const void* u, void* y, void* stream);
+int rwkvb200_wkv6_backward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                           const void* v, const float* w, const void* u, const void* gy,
+                           void* gr, void* gk, void* gv, void* gw, void* gu, void* scratch,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * RWKV-6 WKV with initial state.  Replaces cuda_forward / cuda_backward of
+ * wkv6_state/cuda/wkv6state_cuda_v1a.cu:295-308 (wkv6state_op.cpp:8-13).
+ *   every tensor in `dtype` including the raw decay w (B,T,C) and the state
+ *   s, gs (B,H,N,N) indexed [value i][key j]; decay = exp(-exp(w)) inside the kernel.
+ * The *_ex forms take the state in fp32, also return the final state sT, and accept its
+ * gradient dsT (sT / dsT may be NULL): the superset needed for state passing.
+ */
+int rwkvb200_wkv6state_forward(int dtype, int B, int T, int C, int H, const void* r,
+                               const void* k, const void* v, const void* w, const void* u,
+                               const void* s, void* y, void* stream);
+int rwkvb200_wkv6state_backward(int dtype, int B, int T, int C, int H, const void* r,
+                                const void* k, const void* v, const void* w, const void* u,
+                                const void* s, const void* gy, void* gr, void* gk, void* gv,
+                                void* gw, void* gu, void* gs, void* scratch, void* stream);
+int rwkvb200_wkv6state_forward_ex(int dtype, int B, int T, int C, int H, const void* r,
+                                  const void* k, const void* v, const void* w, const void* u,
+                                  const float* s0, void* y, float* sT, void* stream);
+int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const void* r,
+                                   const void* k, const void* v, const void* w, const void* u,
+                                   const float* s0, const void* gy, const float* dsT, void* gr,
+                                   void* gk, void* gv, void* gw, void* gu, float* ds0,
+                                   void* scratch, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * RWKV-7 generalised delta rule with soft-clamped decay, bf16 or fp32 activations.
+ * One pair of entry points serves the three reference operators:
+ *   rwkv7_clampw              cuda_forward/backward, rwkv7_fast_fused/cuda/rwkv7_clampw.cu:76-79,172-176
+ *                             (rwkv7_clampw.cpp:12-24):        s0 = sT = dsT = ds0 = NULL
+ *   rwkv7_state_clampw        rwkv7_state_clampw.cu (rwkv7_state_clampw.cpp:12-24):  sT = dsT = NULL
+ *   rwkv7_statepassing_clampw rwkv7_statepassing_clampw.cu:82-85,189-193
+ *                             (rwkv7_statepassing_clampw.cpp:12-24): all four given
+ *   r,w,k,v,a,b,y,dy,dr..db (B,T,H,N) in `dtype` (w is the raw decay input; the kernel
+ *   computes exp(-e^{-0.5} sigmoid(w))); s0,sT,dsT,ds0 (B,H,N,N) fp32 indexed
+ *   [value i][key j].
+ *   s  (B,H,T/chunk_len,N,N) fp32 and sa (B,T,H,N) fp32 are the saved-for-backward buffers
+ *   the reference harness allocates; forward fills them, backward reads them, their internal
+ *   layout is private to this library.  T must be a multiple of chunk_len (reference: 16).
+ */
+int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int chunk_len, const float* s0,
+                          const void* r, const void* w, const void* k, const void* v,
+                          const void* a, const void* b, void* y, float* sT, float* s, float* sa,
+                          void* stream);
+int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len, const void* r,
+                           const void* w, const void* k, const void* v, const void* a,
+                           const void* b, const void* dy, const float* dsT, const float* s,
+                           const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv,
+                           void* da, void* db, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKVB200_H */

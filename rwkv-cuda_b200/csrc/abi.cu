@@ -1,0 +1,78 @@
+// Error plumbing, library identity and the RWKV-7 entry points (argument checks + dispatch
+// between the general-shape kernels and the N = 64 tensor-core path).
+#include "common.cuh"
+#include "wkv7_dispatch.cuh"
+
+namespace rwkvb200 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("%s: kernel launch failed: %s", what, cudaGetErrorString(e));
+        return RWKVB200_ECUDA;
+    }
+    return RWKVB200_OK;
+}
+
+}  // namespace rwkvb200
+
+using namespace rwkvb200;
+
+extern "C" const char* rwkvb200_strerror(int code) {
+    switch (code) {
+        case RWKVB200_OK: return "ok";
+        case RWKVB200_EINVAL: return "invalid argument";
+        case RWKVB200_ENULL: return "null pointer";
+        case RWKVB200_EALIGN: return "misaligned pointer";
+        case RWKVB200_EUNSUPPORTED: return "unsupported configuration";
+        case RWKVB200_ECUDA: return "CUDA error";
+        default: return "unknown error";
+    }
+}
+
+extern "C" const char* rwkvb200_last_error(void) { return g_err; }
+extern "C" int rwkvb200_version(void) { return 100; }
+extern "C" int rwkvb200_built_for_sm(void) { return 100; }
+
+static int wkv7_check(const char* what, int dtype, int B, int T, int H, int N, int chunk) {
+    RWKV_REQUIRE(dtype == RWKVB200_F32 || dtype == RWKVB200_BF16, RWKVB200_EINVAL, "%s: unknown dtype %d", what, dtype);
+    RWKV_REQUIRE(B > 0 && T > 0 && H > 0 && N > 0 && chunk > 0, RWKVB200_EINVAL,
+                 "%s: B=%d T=%d H=%d N=%d chunk_len=%d must be positive", what, B, T, H, N, chunk);
+    RWKV_REQUIRE(B <= 65535, RWKVB200_EINVAL, "%s: B=%d exceeds 65535", what, B);
+    RWKV_REQUIRE(N <= RWKVB200_MAX_HEAD_SIZE, RWKVB200_EUNSUPPORTED, "%s: head size %d > %d", what, N,
+                 RWKVB200_MAX_HEAD_SIZE);
+    RWKV_REQUIRE(T % chunk == 0, RWKVB200_EINVAL, "%s: T=%d is not a multiple of chunk_len=%d", what, T, chunk);
+    return RWKVB200_OK;
+}
+
+extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int chunk_len, const float* s0,
+                                     const void* r, const void* w, const void* k, const void* v, const void* a,
+                                     const void* b, void* y, float* sT, float* s, float* sa, void* stream) {
+    if (int e = wkv7_check("wkv7_forward", dtype, B, T, H, N, chunk_len)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(w); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(a); RWKV_NOTNULL(b);
+    RWKV_NOTNULL(y);
+    RWKV_REQUIRE((s == nullptr) == (sa == nullptr), RWKVB200_EINVAL,
+                 "wkv7_forward: s and sa must be given together (or both NULL for inference)");
+    return wkv7_generic_forward(dtype, B, T, H, N, chunk_len, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
+}
+
+extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len, const void* r,
+                                      const void* w, const void* k, const void* v, const void* a, const void* b,
+                                      const void* dy, const float* dsT, const float* s, const float* sa, float* ds0,
+                                      void* dr, void* dw, void* dk, void* dv, void* da, void* db, void* stream) {
+    if (int e = wkv7_check("wkv7_backward", dtype, B, T, H, N, chunk_len)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(w); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(a); RWKV_NOTNULL(b);
+    RWKV_NOTNULL(dy); RWKV_NOTNULL(s); RWKV_NOTNULL(sa);
+    RWKV_NOTNULL(dr); RWKV_NOTNULL(dw); RWKV_NOTNULL(dk); RWKV_NOTNULL(dv); RWKV_NOTNULL(da); RWKV_NOTNULL(db);
+    return wkv7_generic_backward(dtype, B, T, H, N, chunk_len, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv,
+                                 da, db, as_stream(stream));
+}

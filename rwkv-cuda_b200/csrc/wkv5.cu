@@ -1,0 +1,312 @@
+// RWKV-5 and RWKV-5a WKV (static per-channel decay), fp32 or bf16 activations, fp32 state.
+//
+// Operator (wkv5/run.py:66-87 and wkv5a/run.py:260-289 of the reference project), per (b,h):
+//   y_t[i] = sum_j r_t[j] ( U[j,i] k_t[j] v_t[i] + S[j,i] ),   S[j,i] <- W[j,i] S[j,i] + k_t[j] v_t[i]
+//   RWKV-5 : W[j,i] = w[j],        U[j,i] = u[j]
+//   RWKV-5a: W[j,i] = w1[j] w2[i], U[j,i] = u1[j] + u2[i]
+// (j = key channel, i = value channel, S starts at zero.)
+//
+// One CTA per (batch, head); thread x owns one line of the N x N state in registers and the
+// per-token vectors it has to see from its neighbours are exchanged through a double-buffered
+// shared-memory stage (one barrier per token); the next token's elements are already in
+// registers while the current one is being processed.
+//
+// Backward, three sweeps over time with at most two state lines per thread:
+//   1. forward, thread = key i:   S[i,:], Z[i,:]  -> gr, gu(1), gw(1)
+//        Z_t = sum_{s<t} (t-1-s) W^{t-1-s} k_s v_s^T obeys Z <- W (Z + S), and
+//        dL/dlog w[i] = sum_t r_t[i] sum_j gy_t[j] Z_t[i,j]: no scratch, no second pass.
+//   1b (RWKV-5a only). forward, thread = value i: S[:,i], Z[:,i] -> gu2, gw2
+//   2. reverse, thread = key i and value i at once: D[i,:] -> gk,  D[:,i] -> gv
+// gw is returned multiplied by ww = -exp(w_raw), gw/gu as per-batch partials (B,C), exactly
+// what the reference kernels hand to their autograd wrappers.
+#include "common.cuh"
+
+namespace rwkvb200 {
+namespace {
+
+template <int NMAX>
+struct __align__(16) Stage {
+    float a[2][NMAX];
+};
+
+// ------------------------------------------------------------------------------------
+template <typename E, int NMAX, bool DUAL>
+__global__ void __launch_bounds__(NMAX) wkv5_forward_kernel(int T, int C, int H, int N, const E* __restrict__ r_,
+                                                           const E* __restrict__ k_, const E* __restrict__ v_,
+                                                           const float* __restrict__ w1_, const E* __restrict__ u1_,
+                                                           const float* __restrict__ w2_, const E* __restrict__ u2_,
+                                                           E* __restrict__ y_) {
+    const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
+    const bool live = i < N;
+    __shared__ Stage<NMAX> rs, ks;
+    __shared__ __align__(16) float ws[NMAX], us[NMAX];
+    ws[i] = live ? w1_[h * N + i] : 0.f;
+    us[i] = live ? to_f(u1_[h * N + i]) : 0.f;
+    const float w2 = (DUAL && live) ? w2_[h * N + i] : 1.f;
+    const float u2 = (DUAL && live) ? to_f(u2_[h * N + i]) : 0.f;
+
+    float S[NMAX];
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) S[j] = 0.f;
+
+    const i64 base = (i64)b * T * C + h * N + i;
+    float rn = live ? to_f(r_[base]) : 0.f, kn = live ? to_f(k_[base]) : 0.f, vn = live ? to_f(v_[base]) : 0.f;
+    for (int t = 0; t < T; ++t) {
+        const int p = t & 1;
+        rs.a[p][i] = rn;
+        ks.a[p][i] = kn;
+        const float v = vn;
+        __syncthreads();
+        if (t + 1 < T && live) {
+            const i64 o = base + (i64)(t + 1) * C;
+            rn = to_f(r_[o]); kn = to_f(k_[o]); vn = to_f(v_[o]);
+        }
+        float y = 0.f;
+#pragma unroll
+        for (int j = 0; j < NMAX; j += 4) {
+            const float4 r4 = *reinterpret_cast<const float4*>(&rs.a[p][j]);
+            const float4 k4 = *reinterpret_cast<const float4*>(&ks.a[p][j]);
+            const float4 w4 = *reinterpret_cast<const float4*>(&ws[j]);
+            const float4 u4 = *reinterpret_cast<const float4*>(&us[j]);
+            const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
+            const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float x = kk[e] * v;
+                y = fmaf(rr[e], fmaf(DUAL ? uu[e] + u2 : uu[e], x, S[j + e]), y);
+                S[j + e] = fmaf(S[j + e], DUAL ? ww[e] * w2 : ww[e], x);
+            }
+        }
+        if (live) y_[base + (i64)t * C] = from_f<E>(y);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+template <typename E, int NMAX, bool DUAL>
+__global__ void __launch_bounds__(NMAX) wkv5_backward_kernel(
+    int T, int C, int H, int N, const E* __restrict__ r_, const E* __restrict__ k_, const E* __restrict__ v_,
+    const float* __restrict__ w1_, const float* __restrict__ ww1_, const E* __restrict__ u1_,
+    const float* __restrict__ w2_, const float* __restrict__ ww2_, const E* __restrict__ u2_,
+    const E* __restrict__ gy_, E* __restrict__ gr_, E* __restrict__ gk_, E* __restrict__ gv_, E* __restrict__ gw1_,
+    E* __restrict__ gu1_, E* __restrict__ gw2_, E* __restrict__ gu2_) {
+    const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
+    const bool live = i < N;
+    __shared__ Stage<NMAX> rs, ks, vs, gs;
+    __shared__ __align__(16) float w1s[NMAX], u1s[NMAX], w2s[NMAX], u2s[NMAX];
+    w1s[i] = live ? w1_[h * N + i] : 0.f;
+    u1s[i] = live ? to_f(u1_[h * N + i]) : 0.f;
+    w2s[i] = (DUAL && live) ? w2_[h * N + i] : (live ? 1.f : 0.f);
+    u2s[i] = (DUAL && live) ? to_f(u2_[h * N + i]) : 0.f;
+    __syncthreads();
+    const float w1 = w1s[i], u1 = u1s[i], w2 = w2s[i], u2 = u2s[i];
+    const i64 base = (i64)b * T * C + h * N + i;
+    const i64 pbase = (i64)b * C + h * N + i;
+
+    float S[NMAX], Z[NMAX];
+
+    // ---- sweep 1: thread = key i, lines over value j -----------------------------------
+    {
+#pragma unroll
+        for (int j = 0; j < NMAX; ++j) S[j] = Z[j] = 0.f;
+        float gu = 0.f, gw = 0.f;
+        float rn = live ? to_f(r_[base]) : 0.f, kn = live ? to_f(k_[base]) : 0.f;
+        float vn = live ? to_f(v_[base]) : 0.f, gn = live ? to_f(gy_[base]) : 0.f;
+        for (int t = 0; t < T; ++t) {
+            const int p = t & 1;
+            vs.a[p][i] = vn;
+            gs.a[p][i] = gn;
+            const float r = rn, k = kn;
+            __syncthreads();
+            if (t + 1 < T && live) {
+                const i64 o = base + (i64)(t + 1) * C;
+                rn = to_f(r_[o]); kn = to_f(k_[o]); vn = to_f(v_[o]); gn = to_f(gy_[o]);
+            }
+            float gr = 0.f, xg = 0.f, zg = 0.f;
+#pragma unroll
+            for (int j = 0; j < NMAX; ++j) {
+                const float x = k * vs.a[p][j], g = gs.a[p][j];
+                const float w = DUAL ? w1 * w2s[j] : w1;
+                gr = fmaf(fmaf(DUAL ? u1 + u2s[j] : u1, x, S[j]), g, gr);
+                xg = fmaf(x, g, xg);
+                zg = fmaf(Z[j], g, zg);
+                Z[j] = w * (Z[j] + S[j]);
+                S[j] = fmaf(S[j], w, x);
+            }
+            if (live) gr_[base + (i64)t * C] = from_f<E>(gr);
+            gu = fmaf(r, xg, gu);
+            gw = fmaf(r, zg, gw);
+        }
+        if (live) {
+            gu1_[pbase] = from_f<E>(gu);
+            gw1_[pbase] = from_f<E>(ww1_[h * N + i] * gw);
+        }
+    }
+
+    // ---- sweep 1b (RWKV-5a): thread = value i, lines over key j ------------------------
+    if (DUAL) {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < NMAX; ++j) S[j] = Z[j] = 0.f;
+        float gu = 0.f, gw = 0.f;
+        float rn = live ? to_f(r_[base]) : 0.f, kn = live ? to_f(k_[base]) : 0.f;
+        float vn = live ? to_f(v_[base]) : 0.f, gn = live ? to_f(gy_[base]) : 0.f;
+        for (int t = 0; t < T; ++t) {
+            const int p = t & 1;
+            rs.a[p][i] = rn;
+            ks.a[p][i] = kn;
+            const float v = vn, g = gn;
+            __syncthreads();
+            if (t + 1 < T && live) {
+                const i64 o = base + (i64)(t + 1) * C;
+                rn = to_f(r_[o]); kn = to_f(k_[o]); vn = to_f(v_[o]); gn = to_f(gy_[o]);
+            }
+            float rk = 0.f, zr = 0.f;
+#pragma unroll
+            for (int j = 0; j < NMAX; ++j) {
+                const float x = v * ks.a[p][j], r = rs.a[p][j];
+                const float w = w1s[j] * w2;
+                rk = fmaf(r, ks.a[p][j], rk);
+                zr = fmaf(Z[j], r, zr);
+                Z[j] = w * (Z[j] + S[j]);
+                S[j] = fmaf(S[j], w, x);
+            }
+            gu = fmaf(g * v, rk, gu);
+            gw = fmaf(g, zr, gw);
+        }
+        if (live) {
+            gu2_[pbase] = from_f<E>(gu);
+            gw2_[pbase] = from_f<E>(ww2_[h * N + i] * gw);
+        }
+    }
+
+    // ---- sweep 2: reverse; S = D[key i, :], Z = D[:, value i] --------------------------
+    {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < NMAX; ++j) S[j] = Z[j] = 0.f;
+        const i64 last = base + (i64)(T - 1) * C;
+        float rn = live ? to_f(r_[last]) : 0.f, kn = live ? to_f(k_[last]) : 0.f;
+        float vn = live ? to_f(v_[last]) : 0.f, gn = live ? to_f(gy_[last]) : 0.f;
+        for (int t = T - 1; t >= 0; --t) {
+            const int p = t & 1;
+            rs.a[p][i] = rn; ks.a[p][i] = kn; vs.a[p][i] = vn; gs.a[p][i] = gn;
+            const float r = rn, g = gn;
+            __syncthreads();
+            if (t > 0 && live) {
+                const i64 o = base + (i64)(t - 1) * C;
+                rn = to_f(r_[o]); kn = to_f(k_[o]); vn = to_f(v_[o]); gn = to_f(gy_[o]);
+            }
+            float gk = 0.f, gv = 0.f;
+#pragma unroll
+            for (int j = 0; j < NMAX; ++j) {
+                const float x = r * gs.a[p][j];    // key i, value j
+                const float x2 = g * rs.a[p][j];   // key j, value i
+                const float wa = DUAL ? w1 * w2s[j] : w1;
+                const float wb = DUAL ? w1s[j] * w2 : w1s[j];
+                gk = fmaf(fmaf(DUAL ? u1 + u2s[j] : u1, x, S[j]), vs.a[p][j], gk);
+                gv = fmaf(fmaf(DUAL ? u1s[j] + u2 : u1s[j], x2, Z[j]), ks.a[p][j], gv);
+                S[j] = fmaf(S[j], wa, x);
+                Z[j] = fmaf(Z[j], wb, x2);
+            }
+            if (live) {
+                gk_[base + (i64)t * C] = from_f<E>(gk);
+                gv_[base + (i64)t * C] = from_f<E>(gv);
+            }
+        }
+    }
+}
+
+template <typename E, bool DUAL>
+int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const float* w1,
+               const void* u1, const float* w2, const void* u2, void* y, cudaStream_t st) {
+    const int N = C / H;
+#define RWKV_GO(NM)                                                                                           \
+    wkv5_forward_kernel<E, NM, DUAL><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, \
+                                                            w1, (const E*)u1, w2, (const E*)u2, (E*)y)
+    switch (head_capacity(N)) {
+        case 32: RWKV_GO(32); break;
+        case 64: RWKV_GO(64); break;
+        default: RWKV_GO(128); break;
+    }
+#undef RWKV_GO
+    return check_launch(DUAL ? "wkv5a_forward" : "wkv5_forward");
+}
+
+template <typename E, bool DUAL>
+int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const float* w1,
+               const float* ww1, const void* u1, const float* w2, const float* ww2, const void* u2, const void* gy,
+               void* gr, void* gk, void* gv, void* gw1, void* gu1, void* gw2, void* gu2, cudaStream_t st) {
+    const int N = C / H;
+#define RWKV_GO(NM)                                                                                              \
+    wkv5_backward_kernel<E, NM, DUAL><<<B * H, NM, 0, st>>>(                                                     \
+        T, C, H, N, (const E*)r, (const E*)k, (const E*)v, w1, ww1, (const E*)u1, w2, ww2, (const E*)u2,         \
+        (const E*)gy, (E*)gr, (E*)gk, (E*)gv, (E*)gw1, (E*)gu1, (E*)gw2, (E*)gu2)
+    switch (head_capacity(N)) {
+        case 32: RWKV_GO(32); break;
+        case 64: RWKV_GO(64); break;
+        default: RWKV_GO(128); break;
+    }
+#undef RWKV_GO
+    return check_launch(DUAL ? "wkv5a_backward" : "wkv5_backward");
+}
+
+int check_dims(const char* what, int dtype, int B, int T, int C, int H) {
+    RWKV_REQUIRE(dtype == RWKVB200_F32 || dtype == RWKVB200_BF16, RWKVB200_EINVAL, "%s: unknown dtype %d", what, dtype);
+    RWKV_REQUIRE(B > 0 && T > 0 && C > 0 && H > 0, RWKVB200_EINVAL, "%s: B=%d T=%d C=%d H=%d must be positive", what, B, T, C, H);
+    RWKV_REQUIRE(C % H == 0, RWKVB200_EINVAL, "%s: C=%d is not a multiple of H=%d", what, C, H);
+    RWKV_REQUIRE(C / H <= RWKVB200_MAX_HEAD_SIZE, RWKVB200_EUNSUPPORTED, "%s: head size %d > %d", what, C / H,
+                 RWKVB200_MAX_HEAD_SIZE);
+    return RWKVB200_OK;
+}
+
+}  // namespace
+}  // namespace rwkvb200
+
+using namespace rwkvb200;
+
+extern "C" int rwkvb200_wkv5_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                     const void* v, const float* w, const void* u, void* y, void* stream) {
+    if (int e = check_dims("wkv5_forward", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(y);
+    return dtype == RWKVB200_F32
+               ? launch_fwd<float, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, as_stream(stream))
+               : launch_fwd<bf16, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, as_stream(stream));
+}
+
+extern "C" int rwkvb200_wkv5_backward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                      const void* v, const float* w, const float* ww, const void* u, const void* gy,
+                                      void* gr, void* gk, void* gv, void* gw, void* gu, void* stream) {
+    if (int e = check_dims("wkv5_backward", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(ww); RWKV_NOTNULL(u);
+    RWKV_NOTNULL(gy); RWKV_NOTNULL(gr); RWKV_NOTNULL(gk); RWKV_NOTNULL(gv); RWKV_NOTNULL(gw); RWKV_NOTNULL(gu);
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
+                                          gw, gu, nullptr, nullptr, as_stream(stream))
+               : launch_bwd<bf16, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
+                                         gw, gu, nullptr, nullptr, as_stream(stream));
+}
+
+extern "C" int rwkvb200_wkv5a_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                      const void* v, const float* w1, const void* u1, const float* w2,
+                                      const void* u2, void* y, void* stream) {
+    if (int e = check_dims("wkv5a_forward", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w1); RWKV_NOTNULL(u1); RWKV_NOTNULL(w2);
+    RWKV_NOTNULL(u2); RWKV_NOTNULL(y);
+    return dtype == RWKVB200_F32 ? launch_fwd<float, true>(B, T, C, H, r, k, v, w1, u1, w2, u2, y, as_stream(stream))
+                                 : launch_fwd<bf16, true>(B, T, C, H, r, k, v, w1, u1, w2, u2, y, as_stream(stream));
+}
+
+extern "C" int rwkvb200_wkv5a_backward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                       const void* v, const float* w1, const float* ww1, const void* u1,
+                                       const float* w2, const float* ww2, const void* u2, const void* gy, void* gr,
+                                       void* gk, void* gv, void* gw1, void* gu1, void* gw2, void* gu2, void* stream) {
+    if (int e = check_dims("wkv5a_backward", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w1); RWKV_NOTNULL(ww1); RWKV_NOTNULL(u1);
+    RWKV_NOTNULL(w2); RWKV_NOTNULL(ww2); RWKV_NOTNULL(u2); RWKV_NOTNULL(gy); RWKV_NOTNULL(gr); RWKV_NOTNULL(gk);
+    RWKV_NOTNULL(gv); RWKV_NOTNULL(gw1); RWKV_NOTNULL(gu1); RWKV_NOTNULL(gw2); RWKV_NOTNULL(gu2);
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float, true>(B, T, C, H, r, k, v, w1, ww1, u1, w2, ww2, u2, gy, gr, gk, gv, gw1, gu1,
+                                         gw2, gu2, as_stream(stream))
+               : launch_bwd<bf16, true>(B, T, C, H, r, k, v, w1, ww1, u1, w2, ww2, u2, gy, gr, gk, gv, gw1, gu1,
+                                        gw2, gu2, as_stream(stream));
+}

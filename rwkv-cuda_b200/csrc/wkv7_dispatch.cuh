@@ -1,0 +1,15 @@
+// Launchers of the RWKV-7 kernels, shared between the entry points and the kernel files.
+#pragma once
+#include "common.cuh"
+
+namespace rwkvb200 {
+
+int wkv7_generic_forward(int dtype, int B, int T, int H, int N, int chunk, const float* s0, const void* r,
+                         const void* w, const void* k, const void* v, const void* a, const void* b, void* y,
+                         float* sT, float* s, float* sa, cudaStream_t st);
+int wkv7_generic_backward(int dtype, int B, int T, int H, int N, int chunk, const void* r, const void* w,
+                          const void* k, const void* v, const void* a, const void* b, const void* dy,
+                          const float* dsT, const float* s, const float* sa, float* ds0, void* dr, void* dw, void* dk,
+                          void* dv, void* da, void* db, cudaStream_t st);
+
+}  // namespace rwkvb200

@@ -1,0 +1,373 @@
+"""GPU parity: every operator of the library, through the C ABI, against the fp64 oracle and
+the golden vectors made from the reference formulas."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import wkv_oracle as O
+from tests import helpers as Hh
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def R():
+    import rwkv_cuda_b200 as R
+    R._lib.lib()  # must load: there is no fallback
+    return R
+
+
+def golden(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    return {k: torch.from_numpy(np.asarray(z[k])) for k in z.files}
+
+
+def sentinel(*shape, dtype=torch.float32):
+    """Output buffers start filled with junk so that unwritten elements show up
+    (the trick of wkv6_state/run.py:102)."""
+    return torch.empty(*shape, dtype=torch.float32, device=DEV).uniform_(-100, 100).to(dtype)
+
+
+# ------------------------------------------------------------------ RWKV-4
+def run_wkv4(R, w_raw, u, k, v, gy):
+    B, T, C = k.shape
+    wd, ud, kd, vd, gd = (x.float().to(DEV).contiguous() for x in (-torch.exp(w_raw.double()), u, k, v, gy))
+    y = sentinel(B, T, C)
+    R.ops.wkv4_forward(B, T, C, wd, ud, kd, vd, y)
+    gw = torch.zeros(B, C, device=DEV)
+    gu = torch.zeros(B, C, device=DEV)
+    gk, gv = sentinel(B, T, C), sentinel(B, T, C)
+    R.ops.wkv4_backward(B, T, C, wd, ud, kd, vd, gd, gw, gu, gk, gv)
+    return y, gw.sum(0), gu.sum(0), gk, gv
+
+
+def test_wkv4_golden(R, golden_dir):
+    g = golden(golden_dir, "wkv4")
+    yy = g["y"].clone().requires_grad_(True)
+    O.strange_loss(yy).backward()
+    y, gw, gu, gk, gv = run_wkv4(R, g["w"], g["u"], g["k"], g["v"], yy.grad)
+    for got, name in ((y, "y"), (gw, "gw"), (gu, "gu"), (gk, "gk"), (gv, "gv")):
+        Hh.assert_close(got, g[name], Hh.TOL_FP32_STRICT, "wkv4 " + name)
+
+
+@pytest.mark.parametrize("B,T,C", [(4, 256, 256), (2, 768, 96), (3, 37, 5), (1, 5000, 33)])
+def test_wkv4_oracle(R, B, T, C):
+    g = Hh.gen(42)
+    w_raw = Hh.rand(g, C, lo=-4, hi=1)
+    u = Hh.rand(g, C, lo=-1, hi=1)
+    k, v, gy = 0.5 * Hh.randn(g, B, T, C), Hh.randn(g, B, T, C), Hh.randn(g, B, T, C)
+    xs = [x.double().requires_grad_(True) for x in (w_raw, u, k, v)]
+    yo = O.wkv4(*xs)
+    yo.backward(gy.double())
+    y, gw, gu, gk, gv = run_wkv4(R, w_raw, u, k, v, gy)
+    for got, want, name in ((y, yo.detach(), "y"), (gw, xs[0].grad, "gw"), (gu, xs[1].grad, "gu"),
+                            (gk, xs[2].grad, "gk"), (gv, xs[3].grad, "gv")):
+        Hh.assert_close(got, want, Hh.TOL_FP32_STRICT, f"wkv4 {name}")
+
+
+def test_wkv4_extreme_values_stay_finite(R):
+    """k in +-1000 overflows the plain formula; the kernel must not (wkv/run.py:157-161)."""
+    g = Hh.gen(1)
+    B, T, C = 2, 64, 32
+    w_raw, u = Hh.rand(g, C, lo=-5, hi=2), Hh.rand(g, C, lo=-10, hi=10)
+    k, v, gy = Hh.rand(g, B, T, C, lo=-1000, hi=1000), Hh.rand(g, B, T, C, lo=-10, hi=10), Hh.randn(g, B, T, C)
+    xs = [x.double().requires_grad_(True) for x in (w_raw, u, k, v)]
+    yo = O.wkv4(*xs)
+    y, gw, gu, gk, gv = run_wkv4(R, w_raw, u, k, v, gy)
+    Hh.assert_close(y, yo.detach(), 1e-4, "wkv4 extreme y")
+    for t in (gw, gu, gk, gv):
+        assert torch.isfinite(t).all()
+
+
+# ------------------------------------------------------------------ depthwise_conv1d
+def run_timex(R, w, k, gy, eps):
+    B, C, T = k.shape
+    wd, kd, gd = (x.float().to(DEV).contiguous() for x in (w, k, gy))
+    x = sentinel(B, C, T)
+    R.ops.timex_forward(wd, kd, x, eps, B, C, T)
+    gw, gk = sentinel(B, C, T), sentinel(B, C, T)
+    R.ops.timex_backward(wd, kd, gd, gw, gk, B, C, T)
+    gws, gk2 = sentinel(C, T), sentinel(B, C, T)
+    R.ops.timex_backward_reduced(wd, kd, gd, gws, gk2, B, C, T)
+    return x, gw.sum(0), gk, gws, gk2
+
+
+def test_timex_golden(R, golden_dir):
+    g = golden(golden_dir, "timex")
+    yy = g["y"].clone().requires_grad_(True)
+    O.strange_loss(yy).backward()
+    x, gw, gk, gws, gk2 = run_timex(R, g["w"], g["k"], yy.grad, float(g["eps"]))
+    for got, name in ((x, "y"), (gw, "gw"), (gk, "gk"), (gws, "gw"), (gk2, "gk")):
+        Hh.assert_close(got, g[name], Hh.TOL_FP32_STRICT, "timex " + name)
+
+
+@pytest.mark.parametrize("B,C,T", [(32, 24, 768), (8, 7, 768), (3, 5, 130), (5, 3, 1), (9, 2, 2048), (1, 4, 63)])
+def test_timex_oracle(R, B, C, T):
+    g = Hh.gen(42)
+    w = Hh.randn(g, C, T) / T ** 0.5
+    k, gy = Hh.randn(g, B, C, T), Hh.randn(g, B, C, T)
+    wl, kl = w.double().requires_grad_(True), k.double().requires_grad_(True)
+    yo = O.timex_conv(wl, kl, 0.1)
+    yo.backward(gy.double())
+    x, gw, gk, gws, gk2 = run_timex(R, w, k, gy, 0.1)
+    for got, want, name in ((x, yo.detach(), "x"), (gw, wl.grad, "gw"), (gk, kl.grad, "gk"),
+                            (gws, wl.grad, "gw(reduced)"), (gk2, kl.grad, "gk(reduced)")):
+        Hh.assert_close(got, want, Hh.TOL_FP32_STRICT, f"timex {name}")
+
+
+# ------------------------------------------------------------------ RWKV-5 / 5a
+def run_wkv5(R, dtype, H, r, k, v, w_raw, u, gy):
+    B, T, C = r.shape
+    rd, kd, vd, ud, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, u, gy))
+    ew = -torch.exp(w_raw.to(dtype).float()).to(DEV).contiguous()
+    eew = torch.exp(ew).contiguous()
+    y = sentinel(B, T, C, dtype=dtype)
+    R.ops.wkv5_forward(B, T, C, H, rd, kd, vd, eew, ud, y)
+    gr, gk, gv = (sentinel(B, T, C, dtype=dtype) for _ in range(3))
+    gw, gu = sentinel(B, C, dtype=dtype), sentinel(B, C, dtype=dtype)
+    R.ops.wkv5_backward(B, T, C, H, rd, kd, vd, eew, ew, ud, gd, gr, gk, gv, gw, gu)
+    return y, gr, gk, gv, gw.float().sum(0), gu.float().sum(0)
+
+
+def test_wkv5_golden(R, golden_dir):
+    g = golden(golden_dir, "wkv5")
+    out = run_wkv5(R, torch.float32, int(g["H"]), g["r"], g["k"], g["v"], g["w"], g["u"], g["gy"])
+    for got, name in zip(out, ("y", "gr", "gk", "gv", "gw", "gu")):
+        Hh.assert_close(got, g[name], Hh.TOL_FP32, "wkv5 " + name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,T,H,N", [(2, 96, 2, 64), (1, 40, 2, 128), (2, 33, 3, 17), (3, 5, 2, 4), (2, 70, 1, 32)])
+def test_wkv5_oracle(R, dtype, B, T, H, N):
+    g = Hh.gen(42)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.rand(g, H, N, lo=-6, hi=-1), Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv5(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv5(R, dtype, H, r, k, v, w_raw, u, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu")):
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv5 {name}")
+
+
+def run_wkv5a(R, dtype, H, r, k, v, w1, u1, w2, u2, gy):
+    B, T, C = r.shape
+    rd, kd, vd, u1d, u2d, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, u1, u2, gy))
+    ew1 = -torch.exp(w1.to(dtype).float()).to(DEV).contiguous()
+    ew2 = -torch.exp(w2.to(dtype).float()).to(DEV).contiguous()
+    eew1, eew2 = torch.exp(ew1).contiguous(), torch.exp(ew2).contiguous()
+    y = sentinel(B, T, C, dtype=dtype)
+    R.ops.wkv5a_forward(B, T, C, H, rd, kd, vd, eew1, u1d, eew2, u2d, y)
+    gr, gk, gv = (sentinel(B, T, C, dtype=dtype) for _ in range(3))
+    gp = [sentinel(B, C, dtype=dtype) for _ in range(4)]
+    R.ops.wkv5a_backward(B, T, C, H, rd, kd, vd, eew1, ew1, u1d, eew2, ew2, u2d, gd, gr, gk, gv, *gp)
+    return [y, gr, gk, gv] + [x.float().sum(0) for x in gp]
+
+
+def test_wkv5a_golden(R, golden_dir):
+    g = golden(golden_dir, "wkv5a")
+    out = run_wkv5a(R, torch.float32, int(g["H"]), *(g[n] for n in ("r", "k", "v", "w1", "u1", "w2", "u2", "gy")))
+    for got, name in zip(out, ("y", "gr", "gk", "gv", "gw1", "gu1", "gw2", "gu2")):
+        Hh.assert_close(got, g[name], Hh.TOL_FP32, "wkv5a " + name)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,T,H,N", [(3, 65, 3, 17), (2, 80, 2, 64), (1, 4, 1, 4)])
+def test_wkv5a_oracle(R, dtype, B, T, H, N):
+    g = Hh.gen(7)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w1, w2 = Hh.rand(g, H, N, lo=-6, hi=-1), Hh.rand(g, H, N, lo=-6, hi=-1)
+    u1, u2, gy = Hh.rand(g, H, N, lo=-1, hi=1), Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w1, u1, w2, u2)]
+    yo = O.wkv5a(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv5a(R, dtype, H, r, k, v, w1, u1, w2, u2, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw1", "gu1", "gw2", "gu2")):
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv5a {name}")
+
+
+# ------------------------------------------------------------------ RWKV-6
+def run_wkv6(R, dtype, H, r, k, v, w_raw, u, gy):
+    B, T, C = r.shape
+    rd, kd, vd, ud, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, u, gy))
+    ew = -torch.exp(w_raw.to(dtype).float()).to(DEV).contiguous()
+    y = sentinel(B, T, C, dtype=dtype)
+    R.ops.wkv6_forward(B, T, C, H, rd, kd, vd, ew, ud, y)
+    gr, gk, gv, gw = (sentinel(B, T, C, dtype=dtype) for _ in range(4))
+    gu = sentinel(B, C, dtype=dtype)
+    R.ops.wkv6_backward(B, T, C, H, rd, kd, vd, ew, ud, gd, gr, gk, gv, gw, gu)
+    return y, gr, gk, gv, gw, gu.float().sum(0)
+
+
+def test_wkv6_golden(R, golden_dir):
+    g = golden(golden_dir, "wkv6")
+    out = run_wkv6(R, torch.float32, int(g["H"]), *(g[n] for n in ("r", "k", "v", "w", "u", "gy")))
+    for got, name in zip(out, ("y", "gr", "gk", "gv", "gw", "gu")):
+        Hh.assert_close(got, g[name], Hh.TOL_FP32, "wkv6 " + name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,T,H,N", [(2, 300, 2, 64), (2, 7, 2, 4), (1, 50, 1, 128), (2, 41, 3, 17)])
+def test_wkv6_oracle(R, dtype, B, T, H, N):
+    """T = 300 is beyond what the reference backward can run (wkv6/run.py:51)."""
+    g = Hh.gen(42)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.randn(g, B, T, C) - 3.0, Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv6(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv6(R, dtype, H, r, k, v, w_raw, u, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu")):
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv6 {name}")
+
+
+# ------------------------------------------------------------------ RWKV-6 with state
+def run_wkv6state(R, dtype, H, r, k, v, w_raw, u, s, gy):
+    B, T, C = r.shape
+    N = C // H
+    rd, kd, vd, wd, ud, sd, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, w_raw, u, s, gy))
+    y = sentinel(B, T, C, dtype=dtype)
+    R.ops.wkv6state_forward(B, T, C, H, rd, kd, vd, wd, ud, sd, y)
+    gr, gk, gv, gw = (sentinel(B, T, C, dtype=dtype) for _ in range(4))
+    gu, gs = sentinel(B, C, dtype=dtype), sentinel(B, H, N, N, dtype=dtype)
+    R.ops.wkv6state_backward(B, T, C, H, rd, kd, vd, wd, ud, sd, gd, gr, gk, gv, gw, gu, gs)
+    return y, gr, gk, gv, gw, gu.float().sum(0), gs
+
+
+def test_wkv6state_golden(R, golden_dir):
+    g = golden(golden_dir, "wkv6state")
+    out = run_wkv6state(R, torch.float32, int(g["H"]), *(g[n] for n in ("r", "k", "v", "w", "u", "s", "gy")))
+    for got, name in zip(out, ("y", "gr", "gk", "gv", "gw", "gu", "gs")):
+        Hh.assert_close(got, g[name], Hh.TOL_FP32, "wkv6state " + name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,T,H,N", [(2, 200, 2, 64), (3, 7, 2, 4)])
+def test_wkv6state_oracle(R, dtype, B, T, H, N):
+    g = Hh.gen(42)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.randn(g, B, T, C) - 3.0, Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    s = 0.1 * Hh.randn(g, B, H, N, N)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u, s)]
+    yo = O.wkv6(*xs[:5], H, s0=xs[5])
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv6state(R, dtype, H, r, k, v, w_raw, u, s, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu", "gs")):
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv6state {name}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_wkv6state_ex_oracle(R, dtype):
+    """fp32 state in, final state out, gradient of the final state in (state passing)."""
+    B, T, H, N = 2, 160, 2, 64
+    g = Hh.gen(5)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.randn(g, B, T, C) - 5.0, Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    s0, dsT = 0.1 * Hh.randn(g, B, H, N, N), Hh.randn(g, B, H, N, N)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)] + [s0.double().requires_grad_(True)]
+    yo, sTo = O.wkv6(*xs[:5], H, s0=xs[5], return_state=True)
+    torch.autograd.backward([yo, sTo], [gy.to(dtype).double(), dsT.double()])
+    rd, kd, vd, wd, ud, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, w_raw, u, gy))
+    s0d, dsTd = s0.to(DEV), dsT.to(DEV)
+    y, sT = sentinel(B, T, C, dtype=dtype), sentinel(B, H, N, N)
+    R.ops.wkv6state_forward_ex(B, T, C, H, rd, kd, vd, wd, ud, s0d, y, sT)
+    gr, gk, gv, gw = (sentinel(B, T, C, dtype=dtype) for _ in range(4))
+    gu, ds0 = sentinel(B, C, dtype=dtype), sentinel(B, H, N, N)
+    R.ops.wkv6state_backward_ex(B, T, C, H, rd, kd, vd, wd, ud, s0d, gd, dsTd, gr, gk, gv, gw, gu, ds0)
+    tol = Hh.tol_for(dtype)
+    wants = [yo.detach(), sTo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip((y, sT, gr, gk, gv, gw, gu.float().sum(0), ds0), wants,
+                               ("y", "sT", "gr", "gk", "gv", "gw", "gu", "ds0")):
+        Hh.assert_close(got, want, tol, f"wkv6state_ex {name}")
+
+
+# ------------------------------------------------------------------ RWKV-7
+def run_wkv7(R, dtype, H, inp, use_s0, use_sT, chunk=16):
+    B, T, C = inp["r"].shape
+    N = C // H
+    d = {n: inp[n].to(dtype).to(DEV).view(B, T, H, N).contiguous() for n in ("r", "w", "k", "v", "a", "b", "dy")}
+    s0 = inp["s0"].float().to(DEV).contiguous() if use_s0 else None
+    dsT = inp["dsT"].float().to(DEV).contiguous() if use_sT else None
+    y = sentinel(B, T, H, N, dtype=dtype)
+    sT = sentinel(B, H, N, N) if use_sT else None
+    s = sentinel(B, H, T // chunk, N, N)
+    sa = sentinel(B, T, H, N)
+    R.ops.wkv7_forward(s0, d["r"], d["w"], d["k"], d["v"], d["a"], d["b"], y, sT, s, sa)
+    grads = [sentinel(B, T, H, N, dtype=dtype) for _ in range(6)]
+    ds0 = sentinel(B, H, N, N) if use_s0 else None
+    R.ops.wkv7_backward(d["r"], d["w"], d["k"], d["v"], d["a"], d["b"], d["dy"], dsT, s, sa, ds0, *grads)
+    out = dict(y=y, sT=sT, ds0=ds0)
+    out.update({n: x for n, x in zip(("dr", "dw", "dk", "dv", "da", "db"), grads)})
+    return out
+
+
+@pytest.mark.parametrize("variant,use_s0,use_sT", [("wkv7_clampw", False, False), ("wkv7_state_clampw", True, False),
+                                                   ("wkv7_statepassing_clampw", True, True)])
+def test_wkv7_golden_fp32(R, golden_dir, variant, use_s0, use_sT):
+    g = golden(golden_dir, variant)
+    H = int(g["H"])
+    out = run_wkv7(R, torch.float32, H, g, use_s0, use_sT)
+    names = ["y", "dr", "dw", "dk", "dv", "da", "db"] + (["ds0"] if use_s0 else []) + (["sT"] if use_sT else [])
+    for n in names:
+        Hh.assert_close(out[n], g[n], Hh.TOL_FP32, f"{variant} {n}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,T,H,N", [(2, 64, 2, 16), (2, 128, 2, 64), (1, 32, 1, 128), (1, 48, 2, 32)])
+@pytest.mark.parametrize("use_s0,use_sT", [(True, True), (False, False), (True, False)])
+def test_wkv7_oracle(R, dtype, B, T, H, N, use_s0, use_sT):
+    inp = Hh.v7_inputs(B, T, H, N)
+    inp64 = {n: (x.to(dtype).double() if n not in ("s0", "dsT") else x.double()) for n, x in inp.items()}
+    want = Hh.v7_oracle(inp64, H, use_s0=use_s0, use_dsT=use_sT)
+    out = run_wkv7(R, dtype, H, inp, use_s0, use_sT)
+    tol = Hh.tol_for(dtype)
+    names = ["y", "dr", "dw", "dk", "dv", "da", "db"] + (["ds0"] if use_s0 else []) + (["sT"] if use_sT else [])
+    for n in names:
+        Hh.assert_close(out[n], want[n], tol, f"wkv7 {n}")
+
+
+def test_wkv7_chunk_len_other_than_16(R):
+    """The checkpoint stride is a runtime value (the reference bakes -D_CHUNK_LEN_ in)."""
+    B, T, H, N = 1, 96, 2, 64
+    inp = Hh.v7_inputs(B, T, H, N, seed=3)
+    inp64 = {n: (x.to(torch.bfloat16).double() if n not in ("s0", "dsT") else x.double()) for n, x in inp.items()}
+    want = Hh.v7_oracle(inp64, H)
+    for chunk in (8, 32):
+        out = run_wkv7(R, torch.bfloat16, H, inp, True, True, chunk=chunk)
+        for n in ("y", "dr", "dw", "dk", "dv", "da", "db", "ds0", "sT"):
+            Hh.assert_close(out[n], want[n], Hh.TOL_BF16, f"wkv7 chunk {chunk} {n}")
+
+
+def test_wkv7_state_passing_composes(R):
+    """Two segments with the state handed over reproduce one pass over the whole sequence
+    (exactly for the state recurrence in fp32, y to bf16 rounding)."""
+    B, T, H, N = 2, 128, 2, 64
+    inp = Hh.v7_inputs(B, T, H, N, seed=11)
+    d = {n: inp[n].to(torch.bfloat16).to(DEV).view(B, T, H, N).contiguous() for n in ("r", "w", "k", "v", "a", "b")}
+    s0 = inp["s0"].to(DEV)
+
+    def fwd(lo, hi, s_in):
+        seg = {n: x[:, lo:hi].contiguous() for n, x in d.items()}
+        y = sentinel(B, hi - lo, H, N, dtype=torch.bfloat16)
+        sT = sentinel(B, H, N, N)
+        R.ops.wkv7_forward(s_in, seg["r"], seg["w"], seg["k"], seg["v"], seg["a"], seg["b"], y, sT, None, None)
+        return y, sT
+
+    y, sT = fwd(0, T, s0)
+    ya, sm = fwd(0, 48, s0)
+    yb, sT2 = fwd(48, T, sm)
+    assert torch.equal(torch.cat([ya, yb], 1), y)
+    assert torch.equal(sT2, sT)
