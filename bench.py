@@ -74,7 +74,7 @@ class V7Workload:
         self.dy, self.s0, self.dsT = self.host_dy.to(dev), self.host_s0.to(dev), self.host_dsT.to(dev)
         self.y = torch.empty(B, T, H, N, dtype=bf, device=dev)
         self.sT = torch.empty(B, H, N, N, device=dev)
-        self.s = torch.empty(B, H, T // 16, N, N, device=dev)
+        self.s = torch.empty(B, H, T // 16, N, N, device=dev)  # saved-for-backward buffers, as the harness allocates them
         self.sa = torch.empty(B, T, H, N, device=dev)
         self.ds0 = torch.empty(B, H, N, N, device=dev)
         self.grads = [torch.empty(B, T, H, N, dtype=bf, device=dev) for _ in range(6)]
@@ -242,6 +242,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
+    ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -261,6 +264,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     W = V7Workload
+    if args.batch or args.seq:  # reduced case for profiler captures; not the benchmark configuration
+        W.B, W.T = args.batch or W.B, args.seq or W.T
+        W.name = f"REDUCED rwkv7_statepassing_clampw fwd+bwd B{W.B} T{W.T} C4096 N64 chunk16"
     assert W.B % world == 0, f"batch {W.B} does not divide over {world} ranks"
     b_local = W.B // world
     wl = W(b_local, dev, rank)
@@ -304,20 +310,22 @@ def main():
     value = tokens_step * args.steps / (ms_total * 1e-3)
 
     # ---- end to end: host buffers through the public API ------------------------------
-    wl.e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.e2e_steps):
+    e2e_val, h2d, d2h = None, 0, 0
+    if not args.no_e2e:
         wl.e2e_step()
-    e1.record()
-    barrier()
-    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_val = tokens_step * args.e2e_steps / (te.item() * 1e-3)
-    h2d, d2h = wl.e2e_bytes()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(args.e2e_steps):
+            wl.e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_val = tokens_step * args.e2e_steps / (te.item() * 1e-3)
+        h2d, d2h = wl.e2e_bytes()
 
     if rank == 0:
         peak, peak_src = hbm_peak()
