@@ -170,6 +170,13 @@ int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len,
                            const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv,
                            void* da, void* db, void* stream);
 
+/* Kernel choice for RWKV-7 (process-wide; set it before launching work, not concurrently with it):
+ * 0 = automatic (tensor-core kernels for bf16, N=64, chunk_len=16; general-shape kernels otherwise),
+ * 1 = general-shape kernels only, 2 = tensor-core kernels only (other shapes are refused).
+ * The forward and the backward of one operator call must run under the same setting: the
+ * layout of s / sa differs between the two kernel families.  No counterpart in the reference. */
+int rwkvb200_wkv7_select_path(int path);
+
 #ifdef __cplusplus
 }
 #endif

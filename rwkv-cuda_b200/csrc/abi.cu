@@ -2,6 +2,7 @@
 // between the general-shape kernels and the N = 64 tensor-core path).
 #include "common.cuh"
 #include "wkv7_dispatch.cuh"
+#include <initializer_list>
 
 namespace rwkvb200 {
 
@@ -43,6 +44,31 @@ extern "C" const char* rwkvb200_last_error(void) { return g_err; }
 extern "C" int rwkvb200_version(void) { return 100; }
 extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 
+// 0 = automatic, 1 = general-shape kernels only, 2 = tensor-core kernels (error if not applicable)
+static int g_wkv7_path = 0;
+
+extern "C" int rwkvb200_wkv7_select_path(int path) {
+    RWKV_REQUIRE(path >= 0 && path <= 2, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..2", path);
+    g_wkv7_path = path;
+    return RWKVB200_OK;
+}
+
+static bool aligned16(std::initializer_list<const void*> ps) {
+    for (const void* p : ps)
+        if (p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) != 0) return false;
+    return true;
+}
+
+// Forward and backward must agree on the layout of the saved buffers, so the choice depends
+// on (dtype, N, chunk_len) only; misaligned tensors on the tensor-core path are an error.
+static int wkv7_use_chunked(const char* what, int dtype, int N, int chunk, bool* use) {
+    const bool shape_ok = dtype == RWKVB200_BF16 && N == 64 && chunk == 16;
+    if (g_wkv7_path == 2)
+        RWKV_REQUIRE(shape_ok, RWKVB200_EUNSUPPORTED, "%s: tensor-core path needs bf16, N=64, chunk_len=16", what);
+    *use = shape_ok && g_wkv7_path != 1;
+    return RWKVB200_OK;
+}
+
 static int wkv7_check(const char* what, int dtype, int B, int T, int H, int N, int chunk) {
     RWKV_REQUIRE(dtype == RWKVB200_F32 || dtype == RWKVB200_BF16, RWKVB200_EINVAL, "%s: unknown dtype %d", what, dtype);
     RWKV_REQUIRE(B > 0 && T > 0 && H > 0 && N > 0 && chunk > 0, RWKVB200_EINVAL,
@@ -62,6 +88,13 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
     RWKV_NOTNULL(y);
     RWKV_REQUIRE((s == nullptr) == (sa == nullptr), RWKVB200_EINVAL,
                  "wkv7_forward: s and sa must be given together (or both NULL for inference)");
+    bool chunked;
+    if (int e = wkv7_use_chunked("wkv7_forward", dtype, N, chunk_len, &chunked)) return e;
+    if (chunked) {
+        RWKV_REQUIRE(aligned16({s0, r, w, k, v, a, b, y, sT, s, sa}), RWKVB200_EALIGN,
+                     "wkv7_forward: the bf16 N=64 path needs 16-byte aligned tensors");
+        return wkv7_chunked_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
+    }
     return wkv7_generic_forward(dtype, B, T, H, N, chunk_len, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
 }
 
@@ -73,6 +106,14 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
     RWKV_NOTNULL(r); RWKV_NOTNULL(w); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(a); RWKV_NOTNULL(b);
     RWKV_NOTNULL(dy); RWKV_NOTNULL(s); RWKV_NOTNULL(sa);
     RWKV_NOTNULL(dr); RWKV_NOTNULL(dw); RWKV_NOTNULL(dk); RWKV_NOTNULL(dv); RWKV_NOTNULL(da); RWKV_NOTNULL(db);
+    bool chunked;
+    if (int e = wkv7_use_chunked("wkv7_backward", dtype, N, chunk_len, &chunked)) return e;
+    if (chunked) {
+        RWKV_REQUIRE(aligned16({r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db}), RWKVB200_EALIGN,
+                     "wkv7_backward: the bf16 N=64 path needs 16-byte aligned tensors");
+        return wkv7_chunked_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
+                                     as_stream(stream));
+    }
     return wkv7_generic_backward(dtype, B, T, H, N, chunk_len, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv,
                                  da, db, as_stream(stream));
 }

@@ -12,4 +12,13 @@ int wkv7_generic_backward(int dtype, int B, int T, int H, int N, int chunk, cons
                           const float* dsT, const float* s, const float* sa, float* ds0, void* dr, void* dw, void* dk,
                           void* dv, void* da, void* db, cudaStream_t st);
 
+// tensor-core path (bf16, head size 64, chunk 16, 16-byte aligned tensors)
+int wkv7_chunked_forward(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k,
+                         const void* v, const void* a, const void* b, void* y, float* sT, float* s, float* sa,
+                         cudaStream_t st);
+int wkv7_chunked_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v,
+                          const void* a, const void* b, const void* dy, const float* dsT, const float* s,
+                          const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,
+                          cudaStream_t st);
+
 }  // namespace rwkvb200
