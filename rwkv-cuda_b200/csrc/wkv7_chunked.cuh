@@ -21,7 +21,7 @@ constexpr int N = 64;     // head size
 constexpr int L = 16;     // chunk length
 constexpr int NT = 128;   // threads per CTA: 4 warps, warp w owns state rows 16w..16w+15
 constexpr int PT = 72;    // pitch (floats) of token-major [16][64] operand arrays
-constexpr int PC = 24;    // pitch (floats) of channel-major [64][16] operand arrays
+constexpr int PK = 68;    // pitch (floats) of token-major arrays that are read along the token index
 constexpr int PU = 24;    // pitch (floats) of the 16x16 matrices
 constexpr int PS = 68;    // pitch (floats) of the [16][64] output staging rows
 constexpr float kWScale = -0.6065306597126334f;  // -exp(-1/2)
@@ -100,6 +100,39 @@ __device__ __forceinline__ void load_a_kmaj(uint32_t (*areg)[4], const float* am
         areg[ks][2] = __float_as_uint(p0[pa]);
         areg[ks][3] = __float_as_uint(p0[pa + 8]);
     }
+}
+
+// Position of channel c (0..7) inside its group of 8 in a channel-permuted array: even channels
+// first.  Reading positions (t, t+4) of such an array yields channels (2t, 2t+1), i.e. the
+// permuted k order, with plain 32-bit loads.
+__device__ __forceinline__ int perm8(int c) { return (c >> 1) + ((c & 1) << 2); }
+
+// A fragments from a row-major [m][k] array whose k positions are channel-permuted.
+template <int KS>
+__device__ __forceinline__ void load_a_plain(uint32_t (*areg)[4], const float* am, int pa, int row0, int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const float* lo = am + (row0 + g) * pa + ks * 8 + t;
+        const float* hi = lo + 8 * pa;
+        areg[ks][0] = __float_as_uint(lo[0]); areg[ks][1] = __float_as_uint(hi[0]);
+        areg[ks][2] = __float_as_uint(lo[4]); areg[ks][3] = __float_as_uint(hi[4]);
+    }
+}
+
+// B from a row-major [k][n] array whose n positions are channel-permuted (element (k, n) at
+// bm[k*pb + 8*(n/8) + perm8(n%8)]).
+template <int NTILES, int KS>
+__device__ __forceinline__ void gemm_rs_kperm(float (*acc)[4], const uint32_t (*areg)[4], const float* bm, int pb,
+                                              int g, int t) {
+    const int gp = perm8(g);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) {
+            const uint32_t b0 = __float_as_uint(bm[(ks * 8 + 2 * t) * pb + nt * 8 + gp]);
+            const uint32_t b1 = __float_as_uint(bm[(ks * 8 + 2 * t + 1) * pb + nt * 8 + gp]);
+            mma8(acc[nt], areg[ks][0], areg[ks][1], areg[ks][2], areg[ks][3], b0, b1);
+        }
 }
 
 // accumulator tiles -> A fragments (rounded to TF32)

@@ -26,18 +26,17 @@ constexpr int PS0 = 72;  // pitch of the staged 64x64 state
 
 struct BwdSmem {
     static constexpr int kRawBytes = 2 * 7 * L * N * 2;              // bf16 [2][7][L*N]: r w k v a b dy
-    static constexpr int kSa = kRawBytes / 4;                        // fp32 [2][L][PT]
-    static constexpr int kS0 = kSa + 2 * L * PT;                     // fp32 [2][N][PS0]
-    static constexpr int kAt = kS0 + 2 * N * PS0;
+    static constexpr int kSa = kRawBytes / 4;                        // fp32 [L][PT]
+    static constexpr int kS0 = kSa + L * PT;                         // fp32 [N][PS0]
+    static constexpr int kAt = kS0 + N * PS0;
     static constexpr int kRt = kAt + L * PT;
     static constexpr int kBt = kRt + L * PT;
     static constexpr int kKt = kBt + L * PT;
     static constexpr int kVf = kKt + L * PT;                         // v, dy as fp32 token-major
     static constexpr int kDy = kVf + L * PT;
     static constexpr int kEv = kDy + L * PT;                         // EV token-major [t][i]
-    static constexpr int kWt = kEv + L * PT;                         // W_t and 1/W_t [t][j]
-    static constexpr int kIw = kWt + L * PT;
-    static constexpr int kU = kIw + L * PT;                          // Uab Uak Ubr Ukr T (natural [s][t])
+    static constexpr int kWt = kEv + L * PT;                         // W_t [t][j]
+    static constexpr int kU = kWt + L * PT;                          // Uab Uak Ubr Ukr T (natural [s][t])
     static constexpr int kP = kU + 5 * L * PU;                       // P1..P4 natural, then transposed
     static constexpr int kWe = kP + 8 * L * PU;
     static constexpr int kHalf = kWe + N;
@@ -47,7 +46,7 @@ struct BwdSmem {
 
 __device__ __forceinline__ void store_bf16(bf16* p, float x) { *p = __float2bfloat16_rn(x); }
 
-__global__ void __launch_bounds__(NT, 1)
+__global__ void __launch_bounds__(NT, 2)
 wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ w_,
                       const bf16* __restrict__ k_, const bf16* __restrict__ v_, const bf16* __restrict__ a_,
                       const bf16* __restrict__ b_, const bf16* __restrict__ dy_, const float* __restrict__ dsT_,
@@ -60,7 +59,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     float *SAs = sm + BwdSmem::kSa, *S0s = sm + BwdSmem::kS0;
     float *At = sm + BwdSmem::kAt, *Rt = sm + BwdSmem::kRt, *Bt = sm + BwdSmem::kBt, *Kt = sm + BwdSmem::kKt;
     float *Vf = sm + BwdSmem::kVf, *dYf = sm + BwdSmem::kDy, *EVs = sm + BwdSmem::kEv;
-    float *Wt = sm + BwdSmem::kWt, *iW = sm + BwdSmem::kIw;
+    float* Wt = sm + BwdSmem::kWt;
     float *Uab = sm + BwdSmem::kU, *Uak = Uab + L * PU, *Ubr = Uak + L * PU, *Ukr = Ubr + L * PU, *Tn = Ukr + L * PU;
     float *Pn = sm + BwdSmem::kP, *Ptr = Pn + 4 * L * PU;   // natural / transposed, index 0..3 = P1..P4
     float *We = sm + BwdSmem::kWe, *Hs = sm + BwdSmem::kHalf;
@@ -87,32 +86,36 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
 
     const int lrow = tid >> 3, lseg = tid & 7;
-    auto issue_loads = [&](int c, int stage) {
+    auto issue_raw = [&](int c, int stage) {
         const i64 off = tok0 + (i64)(c * L + lrow) * C + lseg * 8;
 #pragma unroll
         for (int x = 0; x < 7; ++x) cp_async16(raw + ((stage * 7 + x) * L + lrow) * N + lseg * 8, src[x] + off);
-        // sa: 16 tokens x 64 fp32 = 256 x 16 B, two per thread
+        cp_async_commit();
+    };
+    // sa (16 x 64 fp32) and the chunk-start state (64 x 64 fp32) are single-buffered: they are
+    // requested as soon as the previous chunk has finished with the buffers
+    auto issue_state = [&](int c) {
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const int idx = tid * 2 + q, row = idx >> 4, seg = idx & 15;
-            cp_async16(SAs + (stage * L + row) * PT + seg * 4, sa_ + tok0 + (i64)(c * L + row) * C + seg * 4);
+            cp_async16(SAs + row * PT + seg * 4, sa_ + tok0 + (i64)(c * L + row) * C + seg * 4);
         }
-        // S0: 64 x 64 fp32 = 1024 x 16 B, eight per thread
         const float* s0g = ck + (i64)c * N * N;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             const int idx = q * NT + tid, row = idx >> 4, seg = idx & 15;
-            cp_async16(S0s + (stage * N + row) * PS0 + seg * 4, s0g + row * N + seg * 4);
+            cp_async16(S0s + row * PS0 + seg * 4, s0g + row * N + seg * 4);
         }
         cp_async_commit();
     };
-    issue_loads(nchunks - 1, (nchunks - 1) & 1);
+    issue_raw(nchunks - 1, (nchunks - 1) & 1);
+    issue_state(nchunks - 1);
 
     for (int c = nchunks - 1; c >= 0; --c) {
         const int stage = c & 1;
-        cp_async_wait<0>();
+        cp_async_wait<1>();   // this chunk's input tiles (the state group may still be in flight)
         __syncthreads();
-        if (c > 0) issue_loads(c - 1, stage ^ 1);
+        if (c > 0) issue_raw(c - 1, stage ^ 1); else cp_async_commit();
         const bf16* R = raw + (stage * 7 + 0) * L * N;
         const bf16* Wr = raw + (stage * 7 + 1) * L * N;
         const bf16* K = raw + (stage * 7 + 2) * L * N;
@@ -120,8 +123,8 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         const bf16* A = raw + (stage * 7 + 4) * L * N;
         const bf16* Bv = raw + (stage * 7 + 5) * L * N;
         const bf16* DY = raw + (stage * 7 + 6) * L * N;
-        const float* SA = SAs + stage * L * PT;
-        const float* S0 = S0s + stage * N * PS0;
+        const float* SA = SAs;
+        const float* S0 = S0s;
 
         // ---- prep -----------------------------------------------------------------------------
         {
@@ -151,7 +154,6 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 Vf[tt * PT + j] = to_f(V[tt * N + j]);
                 dYf[tt * PT + j] = to_f(DY[tt * N + j]);
                 Wt[tt * PT + j] = wt;
-                iW[tt * PT + j] = iw;
                 wprev = wt;
             }
         }
@@ -205,9 +207,17 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 mma8(X2[2 + nt], a0, a1, a2, a3, bk.x, bk.y);
             }
         }
+        cp_async_wait<1>();   // sa and the chunk-start state have landed (only the next input tiles may be pending)
         __syncthreads();
 
         // ---- EV and dV ------------------------------------------------------------------------
+        {   // sa arrived as fp32: round it to TF32 once (it is only ever an MMA operand here)
+            float4* p = reinterpret_cast<float4*>(SAs + lrow * PT + lseg * 8);
+            float4 x0 = p[0], x1 = p[1];
+            x0.x = tf32f(x0.x); x0.y = tf32f(x0.y); x0.z = tf32f(x0.z); x0.w = tf32f(x0.w);
+            x1.x = tf32f(x1.x); x1.y = tf32f(x1.y); x1.z = tf32f(x1.z); x1.w = tf32f(x1.w);
+            p[0] = x0; p[1] = x1;
+        }
         uint32_t dyreg[2][4], xreg[2][4], evreg[2][4];
         load_a_kmaj<2>(dyreg, dYf, PT, row0, g, t);          // A[m=i][k=u] = dy_u[i]
         gemm_rs<2, 2>(X2, dyreg, Ubr, PU, g, t);             // += dY U_br^T   (B[k=u][n=t] = U_br[t][u])
@@ -262,7 +272,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const uint2 bv = lds2(Vf + (nt * 8 + g) * PT + ks * 8 + 2 * t);
                 mma8(Z1[nt], a0, a1, a2, a3, bv.x, bv.y);
                 const uint2 bs = lds2(SA + (nt * 8 + g) * PT + ks * 8 + 2 * t);
-                mma8(Z1[2 + nt], a0, a1, a2, a3, tf32(__uint_as_float(bs.x)), tf32(__uint_as_float(bs.y)));
+                mma8(Z1[2 + nt], a0, a1, a2, a3, bs.x, bs.y);
                 const uint2 be = lds2(EVs + (nt * 8 + g) * PT + ks * 8 + 2 * t);
                 mma8(Z2[nt], s0a, s1a, s2a, s3a, be.x, be.y);
                 const uint2 bd = lds2(dYf + (nt * 8 + g) * PT + ks * 8 + 2 * t);
@@ -272,21 +282,42 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
 
         // ---- dK' dB' (in Z1) and dA' dR' (in Z2) ------------------------------------------------
+        // The scaled vectors enter these last small products unrounded (hi + lo TF32 parts, two MMAs):
+        // their rounding error is what the decay gradient's running sum would otherwise amplify.
         uint32_t atreg[2][4], rtreg[2][4], btreg[2][4], ktreg[2][4];
-        load_a_kmaj<2>(atreg, At, PT, row0, g, t);           // A[m=j][k=u] = a~_u[j]
-        load_a_kmaj<2>(rtreg, Rt, PT, row0, g, t);
-        load_a_kmaj<2>(btreg, Bt, PT, row0, g, t);
-        load_a_kmaj<2>(ktreg, Kt, PT, row0, g, t);
+        uint32_t atlo[2][4], rtlo[2][4], btlo[2][4], ktlo[2][4];
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
+                const float wu = Wt[u * PT + j], iwu = __frcp_rn(wu);
+                const float wp = u > 0 ? Wt[(u - 1) * PT + j] : 1.f;
+                const float xa = to_f(A[u * N + j]) * wp, xr = to_f(R[u * N + j]) * wu;
+                const float xb = to_f(Bv[u * N + j]) * iwu, xk = to_f(K[u * N + j]) * iwu;
+                atreg[ks][e] = tf32(xa); atlo[ks][e] = tf32(xa - __uint_as_float(atreg[ks][e]));
+                rtreg[ks][e] = tf32(xr); rtlo[ks][e] = tf32(xr - __uint_as_float(rtreg[ks][e]));
+                btreg[ks][e] = tf32(xb); btlo[ks][e] = tf32(xb - __uint_as_float(btreg[ks][e]));
+                ktreg[ks][e] = tf32(xk); ktlo[ks][e] = tf32(xk - __uint_as_float(ktreg[ks][e]));
+            }
         const float *P1n = Pn, *P2n = Pn + L * PU, *P3n = Pn + 2 * L * PU, *P4n = Pn + 3 * L * PU;
         const float *P1t = Ptr, *P2t = Ptr + L * PU, *P3t = Ptr + 2 * L * PU, *P4t = Ptr + 3 * L * PU;
         gemm_rs<2, 2>(Z1, atreg, P1t, PU, g, t);             // dK' += A~^T P1 + R~^T P2  (B[k=u][n=t] = P[u][t])
+        gemm_rs<2, 2>(Z1, atlo, P1t, PU, g, t);
         gemm_rs<2, 2>(Z1, rtreg, P2t, PU, g, t);
+        gemm_rs<2, 2>(Z1, rtlo, P2t, PU, g, t);
         gemm_rs<2, 2>(Z1 + 2, atreg, P3t, PU, g, t);         // dB'
+        gemm_rs<2, 2>(Z1 + 2, atlo, P3t, PU, g, t);
         gemm_rs<2, 2>(Z1 + 2, rtreg, P4t, PU, g, t);
+        gemm_rs<2, 2>(Z1 + 2, rtlo, P4t, PU, g, t);
         gemm_rs<2, 2>(Z2, btreg, P3n, PU, g, t);             // dA' += B~^T P3^T + K~^T P1^T (B[k=s][n=t] = P[t][s])
+        gemm_rs<2, 2>(Z2, btlo, P3n, PU, g, t);
         gemm_rs<2, 2>(Z2, ktreg, P1n, PU, g, t);
+        gemm_rs<2, 2>(Z2, ktlo, P1n, PU, g, t);
         gemm_rs<2, 2>(Z2 + 2, btreg, P4n, PU, g, t);         // dR'
+        gemm_rs<2, 2>(Z2 + 2, btlo, P4n, PU, g, t);
         gemm_rs<2, 2>(Z2 + 2, ktreg, P2n, PU, g, t);
+        gemm_rs<2, 2>(Z2 + 2, ktlo, P2n, PU, g, t);
 
         // ---- E and ET updates ------------------------------------------------------------------
         gemm_rs_kmaj<8, 2>(E, evreg, At, PT, g, t);          // E += EV A~   (B[k=t][n=j] = a~_t[j])
@@ -308,13 +339,15 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             A0[h2] += __shfl_xor_sync(0xffffffffu, A0[h2], 1);
             A0[h2] += __shfl_xor_sync(0xffffffffu, A0[h2], 2);
         }
+        __syncthreads();      // every warp is done with sa and the staged state
+        if (c > 0) issue_state(c - 1); else cp_async_commit();
         float cterm[2][4], ada[2][4], sgd[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                const float wt = Wt[tt * PT + j], iw = iW[tt * PT + j];
+                const float wt = Wt[tt * PT + j], iw = __frcp_rn(wt);
                 const float wprev = tt > 0 ? Wt[(tt - 1) * PT + j] : 1.f;
                 const float dk = Z1[nt][e] * iw, db = Z1[2 + nt][e] * iw;
                 const float da = Z2[nt][e] * wprev, dr = Z2[2 + nt][e] * wt;

@@ -23,14 +23,12 @@ namespace v7c {
 struct FwdSmem {
     static constexpr int kRaw = 0;                                   // bf16 [2][6][L*N]
     static constexpr int kRawBytes = 2 * 6 * L * N * 2;
-    static constexpr int kAt = kRawBytes / 4;                        // a~ token-major [L][PT]
-    static constexpr int kRt = kAt + L * PT;
-    static constexpr int kBt = kRt + L * PT;                         // b~; reused as y staging [L][PS]
-    static constexpr int kKt = kBt + L * PT;                         // k~; reused as sa staging
-    static constexpr int kBh = kKt + L * PT;                         // b^ channel-major [N][PC]
-    static constexpr int kKh = kBh + N * PC;
-    static constexpr int kVc = kKh + N * PC;
-    static constexpr int kUab = kVc + N * PC;                        // [s][t], fp32
+    static constexpr int kAt = kRawBytes / 4;                        // a~ token-major [L][PT]; reused as y staging
+    static constexpr int kRt = kAt + L * PT;                         // r~;                     reused as sa staging
+    static constexpr int kBt = kRt + L * PT;                         // b~ token-major [L][PK], channels permuted
+    static constexpr int kKt = kBt + L * PK;                         // k~
+    static constexpr int kVf = kKt + L * PK;                         // v as fp32, token-major [L][PK]
+    static constexpr int kUab = kVf + L * PK;                        // [s][t], fp32
     static constexpr int kUak = kUab + L * PU;                       // [t][s], tf32
     static constexpr int kUbr = kUak + L * PU;
     static constexpr int kUkr = kUbr + L * PU;
@@ -42,7 +40,7 @@ struct FwdSmem {
 };
 static_assert(L * PS <= L * PT, "staging must fit in the arrays it reuses");
 
-__global__ void __launch_bounds__(NT, 3)
+__global__ void __launch_bounds__(NT, 4)
 wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __restrict__ r_,
                      const bf16* __restrict__ w_, const bf16* __restrict__ k_, const bf16* __restrict__ v_,
                      const bf16* __restrict__ a_, const bf16* __restrict__ b_, bf16* __restrict__ y_,
@@ -51,10 +49,10 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     float* sm = reinterpret_cast<float*>(smem_raw);
     bf16* raw = reinterpret_cast<bf16*>(smem_raw);
     float *At = sm + FwdSmem::kAt, *Rt = sm + FwdSmem::kRt, *Bt = sm + FwdSmem::kBt, *Kt = sm + FwdSmem::kKt;
-    float *Bh = sm + FwdSmem::kBh, *Kh = sm + FwdSmem::kKh, *Vc = sm + FwdSmem::kVc;
+    float* Vf = sm + FwdSmem::kVf;
     float *Uab = sm + FwdSmem::kUab, *Uak = sm + FwdSmem::kUak, *Ubr = sm + FwdSmem::kUbr, *Ukr = sm + FwdSmem::kUkr;
     float *Tt = sm + FwdSmem::kTt, *We = sm + FwdSmem::kWe, *Hs = sm + FwdSmem::kHalf;
-    float *ystage = Bt, *sastage = Kt;
+    float *ystage = At, *sastage = Rt;
 
     const int hh = blockIdx.x, bb = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -114,31 +112,21 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             __syncthreads();
             const float base = hf ? Hs[j] : 0.f;
             const float lam_e = Hs[j] + Hs[N + j];
-            const float we = __expf(lam_e);
-            if (hf == 0) We[j] = we;
+            if (hf == 0) We[j] = __expf(lam_e);
             float wprev = hf ? __expf(base) : 1.f;
-            float bh[8], kh[8], vc[8];
+            const int jp = (j & ~7) + perm8(j & 7);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
                 const float wt = __expf(lam), iw = __expf(-lam);
-                const float bq = to_f(Bv[tt * N + j]), kq = to_f(K[tt * N + j]);
                 At[tt * PT + j] = tf32f(to_f(A[tt * N + j]) * wprev);
                 Rt[tt * PT + j] = tf32f(to_f(R[tt * N + j]) * wt);
-                Bt[tt * PT + j] = tf32f(bq * iw);
-                Kt[tt * PT + j] = tf32f(kq * iw);
-                bh[q] = tf32f(bq * iw * we);
-                kh[q] = tf32f(kq * iw * we);
-                vc[q] = to_f(V[tt * N + j]);
+                Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * N + j]) * iw);
+                Kt[tt * PK + jp] = tf32f(to_f(K[tt * N + j]) * iw);
+                Vf[tt * PK + j] = to_f(V[tt * N + j]);
                 wprev = wt;
             }
-            float4* pb = reinterpret_cast<float4*>(Bh + j * PC + t0);
-            float4* pk = reinterpret_cast<float4*>(Kh + j * PC + t0);
-            float4* pv = reinterpret_cast<float4*>(Vc + j * PC + t0);
-            pb[0] = make_float4(bh[0], bh[1], bh[2], bh[3]); pb[1] = make_float4(bh[4], bh[5], bh[6], bh[7]);
-            pk[0] = make_float4(kh[0], kh[1], kh[2], kh[3]); pk[1] = make_float4(kh[4], kh[5], kh[6], kh[7]);
-            pv[0] = make_float4(vc[0], vc[1], vc[2], vc[3]); pv[1] = make_float4(vc[4], vc[5], vc[6], vc[7]);
         }
         __syncthreads();
 
@@ -147,7 +135,7 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             const float* Am = (warp & 1) ? Kt : Bt;
             const float* Bm = (warp & 2) ? Rt : At;
             uint32_t areg[8][4];
-            load_a<8>(areg, Am, PT, 0, g, t);
+            load_a_plain<8>(areg, Am, PK, 0, g, t);
             float U[2][4] = {};
             gemm_rs<2, 8>(U, areg, Bm, PT, g, t);
             float* dst = warp == 0 ? Uab : warp == 1 ? Uak : warp == 2 ? Ubr : Ukr;
@@ -185,7 +173,7 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
 
         // ---- the state chain -------------------------------------------------------------------
         uint32_t vreg[2][4], xreg[2][4], sareg[2][4];
-        load_a<2>(vreg, Vc, PC, row0, g, t);
+        load_a_kmaj<2>(vreg, Vf, PK, row0, g, t);
         gemm_rs<2, 2>(X, vreg, Uak, PU, g, t);           // X_a += V U_ak
         acc_to_a<2>(xreg, X);
         float SA[2][4] = {};
@@ -202,13 +190,13 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
                 *reinterpret_cast<float2*>(dst + (row0 + g + 8) * N + nt * 8 + 2 * t) = make_float2(S[nt][2], S[nt][3]);
             }
         }
+        gemm_rs_kperm<8, 2>(S, sareg, Bt, PK, g, t);      // S = (S + SA B~ + V K~) diag(We)
+        gemm_rs_kperm<8, 2>(S, vreg, Kt, PK, g, t);
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {                 // S = S diag(We) + SA B^ + V K^
+        for (int nt = 0; nt < 8; ++nt) {
             const float2 we = *reinterpret_cast<const float2*>(We + nt * 8 + 2 * t);
             S[nt][0] *= we.x; S[nt][1] *= we.y; S[nt][2] *= we.x; S[nt][3] *= we.y;
         }
-        gemm_rs<8, 2>(S, sareg, Bh, PC, g, t);
-        gemm_rs<8, 2>(S, vreg, Kh, PC, g, t);
 
         // ---- y and sa: transpose through shared memory, then full-row stores -------------------
 #pragma unroll
@@ -253,7 +241,7 @@ int wkv7_chunked_forward(int B, int T, int H, const float* s0, const void* r, co
                          const void* v, const void* a, const void* b, void* y, float* sT, float* s, float* sa,
                          cudaStream_t st) {
     using namespace v7c;
-    static_assert(FwdSmem::kBytes <= 75 * 1024, "forward shared memory must allow 3 CTAs per SM");
+    static_assert(FwdSmem::kBytes <= 55 * 1024 + 768, "forward shared memory must allow 4 CTAs per SM");
     cudaError_t e = cudaFuncSetAttribute(wkv7c_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv7_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     dim3 grid(H, B);
