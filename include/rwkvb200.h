@@ -121,6 +121,23 @@ int rwkvb200_wkv6_backward(int dtype, int B, int T, int C, int H, const void* r,
                            void* gr, void* gk, void* gv, void* gw, void* gu, void* scratch,
                            void* stream);
 
+/* RWKV-6 backward for callers that cannot allocate device memory (no counterpart in the
+ * reference).  Same operator and arguments as rwkvb200_wkv6_backward minus `scratch`: the
+ * intermediate buffer is a fixed 32 MiB array inside the library image, so B*T*C must not
+ * exceed rwkvb200_wkv6_backward_noalloc_max_elems() (8 Mi elements); larger problems are
+ * refused with RWKVB200_EINVAL.  The call allocates and frees nothing.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current); make that first call outside of any stream capture.
+ *   - All calls share the one array and it keeps whatever the last call left in it; the kernel
+ *     overwrites what it uses, so nothing needs clearing, but two calls whose kernels overlap
+ *     on the GPU (different streams) race on it: serialise them.
+ */
+size_t rwkvb200_wkv6_backward_noalloc_max_elems(void);
+int rwkvb200_wkv6_backward_noalloc(int dtype, int B, int T, int C, int H, const void* r,
+                                   const void* k, const void* v, const float* w, const void* u,
+                                   const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                                   void* stream);
+
 /* ---------------------------------------------------------------------------------
  * RWKV-6 WKV with initial state.  Replaces cuda_forward / cuda_backward of
  * wkv6_state/cuda/wkv6state_cuda_v1a.cu:295-308 (wkv6state_op.cpp:8-13).

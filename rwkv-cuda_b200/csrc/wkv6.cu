@@ -312,6 +312,59 @@ extern "C" int rwkvb200_wkv6_backward(int dtype, int B, int T, int C, int H, con
                                   nullptr, kNone, scratch, as_stream(stream), "wkv6_backward");
 }
 
+// ---- backward without a scratch argument ---------------------------------------------------
+// Some callers of this library are not allowed to allocate device memory at the point where
+// they run the backward: a latency-critical host thread that must never enter the device
+// allocator, an embedding runtime that owns all device memory and hands out fixed buffers only,
+// a process whose memory pool is already fully committed.  For them the P_t buffer lives in a
+// fixed array that is part of the loaded library image (every GPU that loads the library keeps
+// these 32 MiB until the process exits).
+namespace rwkvb200 {
+namespace {
+constexpr size_t kNoAllocMaxElems = size_t(8) << 20;  // B*T*C limit: 8 Mi floats = 32 MiB
+static __device__ __align__(256) float g_wkv6_noalloc_scratch[kNoAllocMaxElems];
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array, per device, filled on first use
+}  // namespace
+}  // namespace rwkvb200
+
+extern "C" size_t rwkvb200_wkv6_backward_noalloc_max_elems(void) { return kNoAllocMaxElems; }
+
+extern "C" int rwkvb200_wkv6_backward_noalloc(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                              const void* v, const float* w, const void* u, const void* gy,
+                                              void* gr, void* gk, void* gv, void* gw, void* gu, void* stream) {
+    if (int e = check_dims("wkv6_backward_noalloc", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(gy);
+    RWKV_NOTNULL(gr); RWKV_NOTNULL(gk); RWKV_NOTNULL(gv); RWKV_NOTNULL(gw); RWKV_NOTNULL(gu);
+    const size_t need = (size_t)B * T * C;
+    RWKV_REQUIRE(need <= kNoAllocMaxElems, RWKVB200_EINVAL,
+                 "wkv6_backward_noalloc: B*T*C = %zu exceeds the built-in scratch of %zu elements; "
+                 "use rwkvb200_wkv6_backward with a caller-provided scratch buffer",
+                 need, kNoAllocMaxElems);
+    int dev = -1;
+    cudaError_t ce = cudaGetDevice(&dev);
+    RWKV_REQUIRE(ce == cudaSuccess && dev >= 0 && dev < kMaxDevices, RWKVB200_ECUDA,
+                 "wkv6_backward_noalloc: cudaGetDevice: %s (device %d)", cudaGetErrorString(ce), dev);
+    float* scratch = g_noalloc_ptr[dev];
+    if (scratch == nullptr) {
+        // In host code the array's name is only a handle; the device address has to be asked for,
+        // once per device, with that device current.
+        void* p = nullptr;
+        ce = cudaGetSymbolAddress(&p, g_wkv6_noalloc_scratch);
+        RWKV_REQUIRE(ce == cudaSuccess && p != nullptr, RWKVB200_ECUDA,
+                     "wkv6_backward_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
+        scratch = static_cast<float*>(p);
+        g_noalloc_ptr[dev] = scratch;
+    }
+    // The kernel writes every scratch element it later reads (same thread, same launch), so
+    // nothing has to be cleared between calls.
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float>(B, T, C, H, r, k, v, w, 0, u, nullptr, kNone, gy, nullptr, gr, gk, gv, gw, gu,
+                                   nullptr, kNone, scratch, as_stream(stream), "wkv6_backward_noalloc")
+               : launch_bwd<bf16>(B, T, C, H, r, k, v, w, 0, u, nullptr, kNone, gy, nullptr, gr, gk, gv, gw, gu,
+                                  nullptr, kNone, scratch, as_stream(stream), "wkv6_backward_noalloc");
+}
+
 extern "C" int rwkvb200_wkv6state_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
                                           const void* v, const void* w, const void* u, const void* s, void* y,
                                           void* stream) {

@@ -181,6 +181,20 @@ def wkv6_backward(B, T, C, H, r, k, v, w, u, gy, gr, gk, gv, gw, gu):
              _stream(r))
 
 
+def wkv6_backward_noalloc(B, T, C, H, r, k, v, w, u, gy, gr, gk, gv, gw, gu):
+    """wkv6_backward for callers that must not allocate: no scratch tensor is created here, the
+    library uses its built-in 32 MiB buffer (B*T*C <= 8 Mi elements, else RwkvB200Error).  Calls
+    that could overlap on the GPU must be serialised by the caller: they share that buffer."""
+    d = r.dtype
+    for t, n, name in ((r, B * T * C, "r"), (k, B * T * C, "k"), (v, B * T * C, "v"), (w, B * T * C, "w"),
+                       (u, C, "u"), (gy, B * T * C, "gy"), (gr, B * T * C, "gr"), (gk, B * T * C, "gk"),
+                       (gv, B * T * C, "gv"), (gw, B * T * C, "gw"), (gu, B * C, "gu")):
+        _numel(t, n, name)
+    with _dev(r, "r"):
+        call("rwkvb200_wkv6_backward_noalloc", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
+             _ptr(w, "w", torch.float32), *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), _stream(r))
+
+
 # ---- RWKV-6 with state (wkv6_state/cuda/wkv6state_op.cpp:8-13) ------------------------
 def wkv6state_forward(B, T, C, H, r, k, v, w, u, s, y):
     d = r.dtype
