@@ -216,7 +216,7 @@ def run_reference_arm(args, rank, world):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    T_cpu = 256
+    T_cpu = args.cpu_seq
     for _ in range(args.warmup):
         cpu_formula_step(T_cpu, threads)
     times = [cpu_formula_step(T_cpu, threads) for _ in range(args.steps)]
@@ -243,6 +243,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-seq", type=int, default=256, help="sequence length of one CPU-baseline step (B=1, C=4096)")
     ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
     ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
     args = ap.parse_args()
@@ -353,7 +354,7 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            T_cpu = 256
+            T_cpu = args.cpu_seq
             cpu_formula_step(64, threads)
             n = 3
             tt = sum(cpu_formula_step(T_cpu, threads) for _ in range(n))
