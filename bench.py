@@ -99,6 +99,10 @@ class V7Workload:
         self.R.ops.wkv7_backward(*self.inp, self.dy, self.dsT, self.s, self.sa, self.ds0, *self.grads)
 
     launches_per_step = 2
+    # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel per token, from the ncu
+    # capture of the reduced case (profiles/wkv7_chunked_fwd_bwd_B8_T1024.md); traffic is
+    # proportional to the token count
+    dram_bytes_per_token_bwd = (1.149444e9 + 0.385793e9) / (8 * 1024)
 
     def e2e_step(self):
         """Host buffers in, host buffers out, through the public operator API."""
@@ -342,7 +346,9 @@ def main():
                        "l2": "inputs (6 x %.0f MB per GPU) exceed the 126 MB L2" % (b_local * W.T * 4096 * 2 / 1e6)},
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
             "roofline": {"bound": "hbm", "kernel": "wkv7 backward", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": W.dram_bytes_per_token_bwd * b_local * W.T,
+                         "traffic_source": "ncu dram__bytes_read+write of the backward at B8 T1024 (profiles/), scaled by tokens",
+                         "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": bb,
                          "fwd": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak,
                                  "algorithmic_bytes_per_launch": fb},

@@ -113,7 +113,6 @@ def test_functions_autograd_classes():
         y64 = ora_fn(*l64)
         O.strange_loss(y.float()).backward()
         # the oracle gets the gradient the bf16 run actually saw, so only the operator is compared
-        gy = torch.autograd.grad(O.strange_loss(y.detach().float().requires_grad_(True)), [])  if False else None
         yy = y.detach().float().cpu().double().requires_grad_(True)
         O.strange_loss(yy).backward()
         y64.backward(yy.grad.to(bf).double().view_as(y64))
