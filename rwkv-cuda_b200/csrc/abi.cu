@@ -44,11 +44,12 @@ extern "C" const char* rwkvb200_last_error(void) { return g_err; }
 extern "C" int rwkvb200_version(void) { return 100; }
 extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 
-// 0 = automatic, 1 = general-shape kernels only, 2 = tensor-core kernels (error if not applicable)
+// 0 = automatic (= 3 where applicable), 1 = general-shape kernels only, 2 = mma.sync chunked kernels,
+// 3 = tcgen05 forward + chunked backward
 static int g_wkv7_path = 0;
 
 extern "C" int rwkvb200_wkv7_select_path(int path) {
-    RWKV_REQUIRE(path >= 0 && path <= 2, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..2", path);
+    RWKV_REQUIRE(path >= 0 && path <= 3, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..3", path);
     g_wkv7_path = path;
     return RWKVB200_OK;
 }
@@ -63,7 +64,7 @@ static bool aligned16(std::initializer_list<const void*> ps) {
 // on (dtype, N, chunk_len) only; misaligned tensors on the tensor-core path are an error.
 static int wkv7_use_chunked(const char* what, int dtype, int N, int chunk, bool* use) {
     const bool shape_ok = dtype == RWKVB200_BF16 && N == 64 && chunk == 16;
-    if (g_wkv7_path == 2)
+    if (g_wkv7_path >= 2)
         RWKV_REQUIRE(shape_ok, RWKVB200_EUNSUPPORTED, "%s: tensor-core path needs bf16, N=64, chunk_len=16", what);
     *use = shape_ok && g_wkv7_path != 1;
     return RWKVB200_OK;
@@ -80,6 +81,8 @@ static int wkv7_check(const char* what, int dtype, int B, int T, int H, int N, i
     return RWKVB200_OK;
 }
 
+extern "C" int rwkvb200_device_status(void) { return wkv7_umma_error(); }
+
 extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int chunk_len, const float* s0,
                                      const void* r, const void* w, const void* k, const void* v, const void* a,
                                      const void* b, void* y, float* sT, float* s, float* sa, void* stream) {
@@ -93,6 +96,8 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
     if (chunked) {
         RWKV_REQUIRE(aligned16({s0, r, w, k, v, a, b, y, sT, s, sa}), RWKVB200_EALIGN,
                      "wkv7_forward: the bf16 N=64 path needs 16-byte aligned tensors");
+        if (g_wkv7_path != 2)   // automatic and 3: the tcgen05 forward
+            return wkv7_umma_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
         return wkv7_chunked_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
     }
     return wkv7_generic_forward(dtype, B, T, H, N, chunk_len, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));

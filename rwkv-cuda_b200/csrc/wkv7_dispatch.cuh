@@ -16,6 +16,11 @@ int wkv7_generic_backward(int dtype, int B, int T, int H, int N, int chunk, cons
 int wkv7_chunked_forward(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k,
                          const void* v, const void* a, const void* b, void* y, float* sT, float* s, float* sa,
                          cudaStream_t st);
+// tcgen05 forward (same saved-buffer layout as the mma.sync chunked kernels) and its error word
+int wkv7_umma_forward(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k,
+                      const void* v, const void* a, const void* b, void* y, float* sT, float* s, float* sa,
+                      cudaStream_t st);
+int wkv7_umma_error();
 int wkv7_chunked_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v,
                           const void* a, const void* b, const void* dy, const float* dsT, const float* s,
                           const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,

@@ -53,7 +53,7 @@ def test_status_codes_without_launch():
     odd = ctypes.c_void_p(18)
     assert L.rwkvb200_wkv7_forward(1, 1, 32, 1, 64, 16, None, odd, *args7[1:], one, None, one, one, None) == -3
     # path selection is range checked, and the tensor-core path refuses other shapes
-    assert L.rwkvb200_wkv7_select_path(5) == -1
+    assert L.rwkvb200_wkv7_select_path(7) == -1
     assert L.rwkvb200_wkv7_select_path(2) == 0
     assert L.rwkvb200_wkv7_forward(0, 1, 32, 1, 64, 16, None, *args7, one, None, one, one, None) == -4
     assert L.rwkvb200_wkv7_select_path(0) == 0

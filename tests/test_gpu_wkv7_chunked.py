@@ -9,13 +9,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture()
-def R():
+@pytest.fixture(params=[2, 3], ids=["mma_sync", "tcgen05_fwd"])
+def R(request):
+    """2 = mma.sync chunked kernels, 3 = tcgen05 forward with the same backward."""
     import rwkv_cuda_b200 as R
     from rwkv_cuda_b200 import _lib
-    _lib.call("rwkvb200_wkv7_select_path", 2)
+    _lib.call("rwkvb200_wkv7_select_path", request.param)
     yield R
     _lib.call("rwkvb200_wkv7_select_path", 0)
+    assert _lib.lib().rwkvb200_device_status() == 0, "a bounded wait expired inside a tcgen05 kernel"
 
 
 @pytest.mark.parametrize("B,T,H", [(1, 16, 1), (2, 64, 2), (1, 512, 3)])
