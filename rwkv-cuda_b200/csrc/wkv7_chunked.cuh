@@ -44,6 +44,11 @@ __device__ __forceinline__ void mma8(float (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Position of channel c (0..7) inside its group of 8 in a channel-permuted array: even channels
+// first.  Reading positions (t, t+4) of such an array yields channels (2t, 2t+1), i.e. the
+// permuted k order, with plain 32-bit loads.
+__device__ __forceinline__ int perm8(int c) { return (c >> 1) + ((c & 1) << 2); }
+
 // Throughout, the contraction index inside one k-step of 8 is permuted so that MMA slot t maps
 // to element 2t and slot t+4 to element 2t+1.  An accumulator tile (d0..d3) is then directly an
 // A fragment (a0=d0, a1=d2, a2=d1, a3=d3), and B / A fragments read from shared memory are one
@@ -61,6 +66,33 @@ __device__ __forceinline__ void gemm_rs(float (*acc)[4], const uint32_t (*areg)[
         for (int nt = 0; nt < NTILES; ++nt) {
             const uint2 b = lds2(bm + (nt * 8 + g) * pb + ks * 8 + 2 * t);
             mma8(acc[nt], areg[ks][0], areg[ks][1], areg[ks][2], areg[ks][3], b.x, b.y);
+        }
+}
+
+// acc += (Ahi + Alo) * B with each B fragment loaded once (B as in gemm_rs).
+template <int NTILES, int KS>
+__device__ __forceinline__ void gemm_rs2(float (*acc)[4], const uint32_t (*ahi)[4], const uint32_t (*alo)[4],
+                                         const float* bm, int pb, int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) {
+            const uint2 b = lds2(bm + (nt * 8 + g) * pb + ks * 8 + 2 * t);
+            mma8(acc[nt], ahi[ks][0], ahi[ks][1], ahi[ks][2], ahi[ks][3], b.x, b.y);
+            mma8(acc[nt], alo[ks][0], alo[ks][1], alo[ks][2], alo[ks][3], b.x, b.y);
+        }
+}
+
+// B from a row-major [n][k] array whose k positions are channel-permuted (plain 32-bit reads).
+template <int NTILES, int KS>
+__device__ __forceinline__ void gemm_rs_plain(float (*acc)[4], const uint32_t (*areg)[4], const float* bm, int pb,
+                                              int g, int t) {
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) {
+            const float* p = bm + (nt * 8 + g) * pb + ks * 8 + t;
+            mma8(acc[nt], areg[ks][0], areg[ks][1], areg[ks][2], areg[ks][3], __float_as_uint(p[0]), __float_as_uint(p[4]));
         }
 }
 
@@ -102,11 +134,6 @@ __device__ __forceinline__ void load_a_kmaj(uint32_t (*areg)[4], const float* am
     }
 }
 
-// Position of channel c (0..7) inside its group of 8 in a channel-permuted array: even channels
-// first.  Reading positions (t, t+4) of such an array yields channels (2t, 2t+1), i.e. the
-// permuted k order, with plain 32-bit loads.
-__device__ __forceinline__ int perm8(int c) { return (c >> 1) + ((c & 1) << 2); }
-
 // A fragments from a row-major [m][k] array whose k positions are channel-permuted.
 template <int KS>
 __device__ __forceinline__ void load_a_plain(uint32_t (*areg)[4], const float* am, int pa, int row0, int g, int t) {
@@ -116,6 +143,21 @@ __device__ __forceinline__ void load_a_plain(uint32_t (*areg)[4], const float* a
         const float* hi = lo + 8 * pa;
         areg[ks][0] = __float_as_uint(lo[0]); areg[ks][1] = __float_as_uint(hi[0]);
         areg[ks][2] = __float_as_uint(lo[4]); areg[ks][3] = __float_as_uint(hi[4]);
+    }
+}
+
+// A fragments of channel rows row0+g / row0+g+8 from a row-major [k][m] array whose m positions are
+// channel-permuted (row0 a multiple of 8).
+template <int KS>
+__device__ __forceinline__ void load_a_kperm(uint32_t (*areg)[4], const float* am, int pa, int row0, int g, int t) {
+    const int gp = perm8(g);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const float* p0 = am + (ks * 8 + 2 * t) * pa + row0 + gp;
+        areg[ks][0] = __float_as_uint(p0[0]);
+        areg[ks][1] = __float_as_uint(p0[8]);
+        areg[ks][2] = __float_as_uint(p0[pa]);
+        areg[ks][3] = __float_as_uint(p0[pa + 8]);
     }
 }
 

@@ -22,21 +22,21 @@
 namespace rwkvb200 {
 namespace v7c {
 
-constexpr int PS0 = 72;  // pitch of the staged 64x64 state
+constexpr int PS0 = 68;  // pitch of the staged 64x64 state (read along its rows' index)
 
 struct BwdSmem {
     static constexpr int kRawBytes = 2 * 7 * L * N * 2;              // bf16 [2][7][L*N]: r w k v a b dy
     static constexpr int kSa = kRawBytes / 4;                        // fp32 [L][PT]
     static constexpr int kS0 = kSa + L * PT;                         // fp32 [N][PS0]
-    static constexpr int kAt = kS0 + N * PS0;
-    static constexpr int kRt = kAt + L * PT;
-    static constexpr int kBt = kRt + L * PT;
-    static constexpr int kKt = kBt + L * PT;
-    static constexpr int kVf = kKt + L * PT;                         // v, dy as fp32 token-major
-    static constexpr int kDy = kVf + L * PT;
-    static constexpr int kEv = kDy + L * PT;                         // EV token-major [t][i]
-    static constexpr int kWt = kEv + L * PT;                         // W_t [t][j]
-    static constexpr int kU = kWt + L * PT;                          // Uab Uak Ubr Ukr T (natural [s][t])
+    static constexpr int kAt = kS0 + N * PS0;                        // token-major, pitch PK, channels permuted:
+    static constexpr int kRt = kAt + L * PK;
+    static constexpr int kBt = kRt + L * PK;
+    static constexpr int kKt = kBt + L * PK;
+    static constexpr int kVf = kKt + L * PK;                         // v, dy as fp32
+    static constexpr int kDy = kVf + L * PK;
+    static constexpr int kEv = kDy + L * PK;                         // EV [t][i]
+    static constexpr int kWt = kEv + L * PK;                         // W_t [t][j], natural order
+    static constexpr int kU = kWt + L * PK;                          // Uab Uak Ubr Ukr T (natural [s][t])
     static constexpr int kP = kU + 5 * L * PU;                       // P1..P4 natural, then transposed
     static constexpr int kWe = kP + 8 * L * PU;
     static constexpr int kHalf = kWe + N;
@@ -142,18 +142,19 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const float base = hf ? Hs[j] : 0.f;
             if (hf == 0) We[j] = __expf(Hs[j] + Hs[N + j]);
             float wprev = hf ? __expf(base) : 1.f;
+            const int jp = (j & ~7) + perm8(j & 7);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
                 const float wt = __expf(lam), iw = __expf(-lam);
-                At[tt * PT + j] = tf32f(to_f(A[tt * N + j]) * wprev);
-                Rt[tt * PT + j] = tf32f(to_f(R[tt * N + j]) * wt);
-                Bt[tt * PT + j] = tf32f(to_f(Bv[tt * N + j]) * iw);
-                Kt[tt * PT + j] = tf32f(to_f(K[tt * N + j]) * iw);
-                Vf[tt * PT + j] = to_f(V[tt * N + j]);
-                dYf[tt * PT + j] = to_f(DY[tt * N + j]);
-                Wt[tt * PT + j] = wt;
+                At[tt * PK + jp] = tf32f(to_f(A[tt * N + j]) * wprev);
+                Rt[tt * PK + jp] = tf32f(to_f(R[tt * N + j]) * wt);
+                Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * N + j]) * iw);
+                Kt[tt * PK + jp] = tf32f(to_f(K[tt * N + j]) * iw);
+                Vf[tt * PK + jp] = to_f(V[tt * N + j]);
+                dYf[tt * PK + jp] = to_f(DY[tt * N + j]);
+                Wt[tt * PK + j] = wt;
                 wprev = wt;
             }
         }
@@ -164,9 +165,9 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const float* Am = (warp & 1) ? Kt : Bt;
             const float* Bm = (warp & 2) ? Rt : At;
             uint32_t areg[8][4];
-            load_a<8>(areg, Am, PT, 0, g, t);
+            load_a_plain<8>(areg, Am, PK, 0, g, t);
             float U[2][4] = {};
-            gemm_rs<2, 8>(U, areg, Bm, PT, g, t);
+            gemm_rs_plain<2, 8>(U, areg, Bm, PK, g, t);
             float* dst = Uab + warp * L * PU;
             const bool strict = warp < 2;
 #pragma unroll
@@ -201,10 +202,10 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const uint32_t a0 = tf32(E[ks][0]), a1 = tf32(E[ks][2]), a2 = tf32(E[ks][1]), a3 = tf32(E[ks][3]);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                const uint2 bb2 = lds2(Bt + (nt * 8 + g) * PT + ks * 8 + 2 * t);
-                mma8(X2[nt], a0, a1, a2, a3, bb2.x, bb2.y);
-                const uint2 bk = lds2(Kt + (nt * 8 + g) * PT + ks * 8 + 2 * t);
-                mma8(X2[2 + nt], a0, a1, a2, a3, bk.x, bk.y);
+                const float* pb = Bt + (nt * 8 + g) * PK + ks * 8 + t;
+                mma8(X2[nt], a0, a1, a2, a3, __float_as_uint(pb[0]), __float_as_uint(pb[4]));
+                const float* pk = Kt + (nt * 8 + g) * PK + ks * 8 + t;
+                mma8(X2[2 + nt], a0, a1, a2, a3, __float_as_uint(pk[0]), __float_as_uint(pk[4]));
             }
         }
         cp_async_wait<1>();   // sa and the chunk-start state have landed (only the next input tiles may be pending)
@@ -219,7 +220,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             p[0] = x0; p[1] = x1;
         }
         uint32_t dyreg[2][4], xreg[2][4], evreg[2][4];
-        load_a_kmaj<2>(dyreg, dYf, PT, row0, g, t);          // A[m=i][k=u] = dy_u[i]
+        load_a_kperm<2>(dyreg, dYf, PK, row0, g, t);         // A[m=i][k=u] = dy_u[i]
         gemm_rs<2, 2>(X2, dyreg, Ubr, PU, g, t);             // += dY U_br^T   (B[k=u][n=t] = U_br[t][u])
         acc_to_a<2>(xreg, X2);
         float EV[2][4] = {};
@@ -233,7 +234,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             for (int e = 0; e < 4; ++e) {
                 const int i = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
                 store_bf16(dv_ + tok0 + (i64)(c * L + tt) * C + i, X2[2 + nt][e]);
-                EVs[tt * PT + i] = tf32f(EV[nt][e]);
+                EVs[tt * PK + (i & ~7) + perm8(i & 7)] = tf32f(EV[nt][e]);
             }
         __syncthreads();
 
@@ -242,9 +243,10 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const float* Am = (warp & 2) ? dYf : EVs;
             const float* Bm = (warp & 1) ? SA : Vf;
             uint32_t areg[8][4];
-            load_a<8>(areg, Am, PT, 0, g, t);
+            load_a_plain<8>(areg, Am, PK, 0, g, t);
             float P[2][4] = {};
-            gemm_rs<2, 8>(P, areg, Bm, PT, g, t);
+            if (warp & 1) gemm_rs<2, 8>(P, areg, Bm, PT, g, t);        // sa: natural order, 64-bit reads
+            else gemm_rs_plain<2, 8>(P, areg, Bm, PK, g, t);
             const int which = (warp == 0) ? 0 : (warp == 2) ? 1 : (warp == 1) ? 2 : 3;  // P1 P2 P3 P4
             const bool strict = !(warp & 2);
             float* pn = Pn + which * L * PU;
@@ -269,14 +271,14 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const uint32_t s0a = tf32(p0[0]), s1a = tf32(p0[8]), s2a = tf32(p0[PS0]), s3a = tf32(p0[PS0 + 8]);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                const uint2 bv = lds2(Vf + (nt * 8 + g) * PT + ks * 8 + 2 * t);
-                mma8(Z1[nt], a0, a1, a2, a3, bv.x, bv.y);
+                const float* pv = Vf + (nt * 8 + g) * PK + ks * 8 + t;
+                mma8(Z1[nt], a0, a1, a2, a3, __float_as_uint(pv[0]), __float_as_uint(pv[4]));
                 const uint2 bs = lds2(SA + (nt * 8 + g) * PT + ks * 8 + 2 * t);
                 mma8(Z1[2 + nt], a0, a1, a2, a3, bs.x, bs.y);
-                const uint2 be = lds2(EVs + (nt * 8 + g) * PT + ks * 8 + 2 * t);
-                mma8(Z2[nt], s0a, s1a, s2a, s3a, be.x, be.y);
-                const uint2 bd = lds2(dYf + (nt * 8 + g) * PT + ks * 8 + 2 * t);
-                mma8(Z2[2 + nt], s0a, s1a, s2a, s3a, bd.x, bd.y);
+                const float* pe = EVs + (nt * 8 + g) * PK + ks * 8 + t;
+                mma8(Z2[nt], s0a, s1a, s2a, s3a, __float_as_uint(pe[0]), __float_as_uint(pe[4]));
+                const float* pd = dYf + (nt * 8 + g) * PK + ks * 8 + t;
+                mma8(Z2[2 + nt], s0a, s1a, s2a, s3a, __float_as_uint(pd[0]), __float_as_uint(pd[4]));
             }
         }
         __syncthreads();
@@ -291,8 +293,8 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
-                const float wu = Wt[u * PT + j], iwu = __frcp_rn(wu);
-                const float wp = u > 0 ? Wt[(u - 1) * PT + j] : 1.f;
+                const float wu = Wt[u * PK + j], iwu = __frcp_rn(wu);
+                const float wp = u > 0 ? Wt[(u - 1) * PK + j] : 1.f;
                 const float xa = to_f(A[u * N + j]) * wp, xr = to_f(R[u * N + j]) * wu;
                 const float xb = to_f(Bv[u * N + j]) * iwu, xk = to_f(K[u * N + j]) * iwu;
                 atreg[ks][e] = tf32(xa); atlo[ks][e] = tf32(xa - __uint_as_float(atreg[ks][e]));
@@ -302,28 +304,20 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
         const float *P1n = Pn, *P2n = Pn + L * PU, *P3n = Pn + 2 * L * PU, *P4n = Pn + 3 * L * PU;
         const float *P1t = Ptr, *P2t = Ptr + L * PU, *P3t = Ptr + 2 * L * PU, *P4t = Ptr + 3 * L * PU;
-        gemm_rs<2, 2>(Z1, atreg, P1t, PU, g, t);             // dK' += A~^T P1 + R~^T P2  (B[k=u][n=t] = P[u][t])
-        gemm_rs<2, 2>(Z1, atlo, P1t, PU, g, t);
-        gemm_rs<2, 2>(Z1, rtreg, P2t, PU, g, t);
-        gemm_rs<2, 2>(Z1, rtlo, P2t, PU, g, t);
-        gemm_rs<2, 2>(Z1 + 2, atreg, P3t, PU, g, t);         // dB'
-        gemm_rs<2, 2>(Z1 + 2, atlo, P3t, PU, g, t);
-        gemm_rs<2, 2>(Z1 + 2, rtreg, P4t, PU, g, t);
-        gemm_rs<2, 2>(Z1 + 2, rtlo, P4t, PU, g, t);
-        gemm_rs<2, 2>(Z2, btreg, P3n, PU, g, t);             // dA' += B~^T P3^T + K~^T P1^T (B[k=s][n=t] = P[t][s])
-        gemm_rs<2, 2>(Z2, btlo, P3n, PU, g, t);
-        gemm_rs<2, 2>(Z2, ktreg, P1n, PU, g, t);
-        gemm_rs<2, 2>(Z2, ktlo, P1n, PU, g, t);
-        gemm_rs<2, 2>(Z2 + 2, btreg, P4n, PU, g, t);         // dR'
-        gemm_rs<2, 2>(Z2 + 2, btlo, P4n, PU, g, t);
-        gemm_rs<2, 2>(Z2 + 2, ktreg, P2n, PU, g, t);
-        gemm_rs<2, 2>(Z2 + 2, ktlo, P2n, PU, g, t);
+        gemm_rs2<2, 2>(Z1, atreg, atlo, P1t, PU, g, t);      // dK' += A~^T P1 + R~^T P2  (B[k=u][n=t] = P[u][t])
+        gemm_rs2<2, 2>(Z1, rtreg, rtlo, P2t, PU, g, t);
+        gemm_rs2<2, 2>(Z1 + 2, atreg, atlo, P3t, PU, g, t);  // dB'
+        gemm_rs2<2, 2>(Z1 + 2, rtreg, rtlo, P4t, PU, g, t);
+        gemm_rs2<2, 2>(Z2, btreg, btlo, P3n, PU, g, t);      // dA' += B~^T P3^T + K~^T P1^T (B[k=s][n=t] = P[t][s])
+        gemm_rs2<2, 2>(Z2, ktreg, ktlo, P1n, PU, g, t);
+        gemm_rs2<2, 2>(Z2 + 2, btreg, btlo, P4n, PU, g, t);  // dR'
+        gemm_rs2<2, 2>(Z2 + 2, ktreg, ktlo, P2n, PU, g, t);
 
         // ---- E and ET updates ------------------------------------------------------------------
-        gemm_rs_kmaj<8, 2>(E, evreg, At, PT, g, t);          // E += EV A~   (B[k=t][n=j] = a~_t[j])
-        gemm_rs_kmaj<8, 2>(E, dyreg, Rt, PT, g, t);          //    + dY R~
-        gemm_rs_kmaj<8, 2>(ET, atreg, EVs, PT, g, t);        // ET += A~^T EV^T (B[k=t][n=i] = e_t[i])
-        gemm_rs_kmaj<8, 2>(ET, rtreg, dYf, PT, g, t);        //     + R~^T dY^T
+        gemm_rs_kperm<8, 2>(E, evreg, At, PK, g, t);         // E += EV A~   (B[k=t][n=j] = a~_t[j])
+        gemm_rs_kperm<8, 2>(E, dyreg, Rt, PK, g, t);         //    + dY R~
+        gemm_rs_kperm<8, 2>(ET, atreg, EVs, PK, g, t);       // ET += A~^T EV^T (B[k=t][n=i] = e_t[i])
+        gemm_rs_kperm<8, 2>(ET, rtreg, dYf, PK, g, t);       //     + R~^T dY^T
 
         // ---- per-token gradients, rows j = row0+g (+8), columns = tokens --------------------------
         float A0[2] = {0.f, 0.f};                            // sum_i E_start[i,j] S0[i,j]
@@ -347,8 +341,8 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                const float wt = Wt[tt * PT + j], iw = __frcp_rn(wt);
-                const float wprev = tt > 0 ? Wt[(tt - 1) * PT + j] : 1.f;
+                const float wt = Wt[tt * PK + j], iw = __frcp_rn(wt);
+                const float wprev = tt > 0 ? Wt[(tt - 1) * PK + j] : 1.f;
                 const float dk = Z1[nt][e] * iw, db = Z1[2 + nt][e] * iw;
                 const float da = Z2[nt][e] * wprev, dr = Z2[2 + nt][e] * wt;
                 const float rr = to_f(R[tt * N + j]), aa = to_f(A[tt * N + j]);
