@@ -45,11 +45,11 @@ extern "C" int rwkvb200_version(void) { return 100; }
 extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 
 // 0 = automatic (= 3 where applicable), 1 = general-shape kernels only, 2 = mma.sync chunked kernels,
-// 3 = tcgen05 forward + chunked backward
+// 3 = tcgen05 forward + chunked backward, 4 = tcgen05 forward and backward
 static int g_wkv7_path = 0;
 
 extern "C" int rwkvb200_wkv7_select_path(int path) {
-    RWKV_REQUIRE(path >= 0 && path <= 3, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..3", path);
+    RWKV_REQUIRE(path >= 0 && path <= 4, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..4", path);
     g_wkv7_path = path;
     return RWKVB200_OK;
 }
@@ -81,7 +81,10 @@ static int wkv7_check(const char* what, int dtype, int B, int T, int H, int N, i
     return RWKVB200_OK;
 }
 
-extern "C" int rwkvb200_device_status(void) { return wkv7_umma_error(); }
+extern "C" int rwkvb200_device_status(void) {
+    const int f = wkv7_umma_error();
+    return f ? f : wkv7_umma_bwd_error();
+}
 
 extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int chunk_len, const float* s0,
                                      const void* r, const void* w, const void* k, const void* v, const void* a,
@@ -116,6 +119,9 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
     if (chunked) {
         RWKV_REQUIRE(aligned16({r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db}), RWKVB200_EALIGN,
                      "wkv7_backward: the bf16 N=64 path needs 16-byte aligned tensors");
+        if (g_wkv7_path == 4)
+            return wkv7_umma_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
+                                      as_stream(stream));
         return wkv7_chunked_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
                                      as_stream(stream));
     }

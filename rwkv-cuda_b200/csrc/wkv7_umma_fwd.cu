@@ -21,16 +21,12 @@
 // of K; piece kc of row r at kc*LBO + r*16 bytes (8-row groups 128 bytes apart = SBO); LBO carries
 // 16 bytes of padding so that the elementwise writers hit distinct banks.
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code and leaves.
-#include "wkv7_chunked.cuh"
+#include "wkv7_umma.cuh"
 #include "wkv7_dispatch.cuh"
 
 namespace rwkvb200 {
 namespace v7u {
 
-using namespace v7c;
-
-constexpr int LBO_T = 32 * 16 + 16;   // token-major operands [32 rows][K=64]: bytes between K pieces
-constexpr int LBO_C = 64 * 16 + 16;   // channel-major operands [64 rows][K=32]
 constexpr int kTmemCols = 128;
 constexpr int kColS = 0, kColX = 64, kColU = 96;
 
@@ -49,55 +45,6 @@ struct Smem {
     static constexpr int kBytes = kBar + 32;
 };
 static_assert(2 * L * PS * 4 <= 2 * 16 * LBO_T, "y/sa staging reuses the token-major operand arrays");
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)(128 >> 4) << 32;       // SBO: 8-row groups are 128 bytes apart
-    d |= (uint64_t)1 << 46;                // descriptor version of sm_100
-    return d;                              // no swizzle, base offset 0
-}
-__device__ __forceinline__ uint32_t umma_idesc(int n) {   // D fp32, A/B tf32, both K-major, M = 64
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | (4u << 24);
-}
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t done = 0;
-    for (int it = 0; it < (1 << 20) && !done; ++it)
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// one 16x256b tile (8 columns) <-> an mma.sync accumulator tile d[4]
-__device__ __forceinline__ void tmem_ld8(float (&d)[4], uint32_t taddr) {
-    asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const float (&d)[4]) {
-    asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "f"(d[0]), "f"(d[1]), "f"(d[2]), "f"(d[3]) : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// byte offset of element (row, k) in a canonical K-major array
-__device__ __forceinline__ int canon(int row, int k, int lbo) { return (k >> 2) * lbo + row * 16 + (k & 3) * 4; }
 
 __global__ void __launch_bounds__(NT, 4)
 wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __restrict__ r_,

@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[2, 3], ids=["mma_sync", "tcgen05_fwd"])
+@pytest.fixture(params=[2, 3, 4], ids=["mma_sync", "tcgen05_fwd", "tcgen05_fwd_bwd"])
 def R(request):
     """2 = mma.sync chunked kernels, 3 = tcgen05 forward with the same backward."""
     import rwkv_cuda_b200 as R
