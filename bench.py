@@ -238,6 +238,151 @@ def run_reference_arm(args, rank, world):
     }), flush=True)
 
 
+
+# --------------------------------------------------------------------------------------
+# the other benchmark configurations (--op): same timing rules, one GPU, no end-to-end leg
+# --------------------------------------------------------------------------------------
+FP32_NOMINAL_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12   # CUDA-core fp32 FMA peak (nominal, not measured)
+
+
+def _time_fb(fwd, bwd, steps, warmup):
+    for _ in range(max(warmup, 3)):
+        fwd(); bwd()
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for e in evs:
+        e[0].record(); fwd(); e[1].record(); bwd(); e[2].record()
+    torch.cuda.synchronize()
+    f = sum(e[0].elapsed_time(e[1]) for e in evs) / steps
+    b = sum(e[1].elapsed_time(e[2]) for e in evs) / steps
+    return f, b
+
+
+def _cpu_time(fn, repeat=2):
+    fn()
+    t0 = time.perf_counter()
+    for _ in range(repeat):
+        fn()
+    return (time.perf_counter() - t0) / repeat
+
+
+def run_secondary(op, args):
+    """BASELINE configurations 1-4.  Prints one JSON line: tokens/s (or rows/s), per-kernel times, the
+    roofline of the backward kernel and the CPU formula path on a bounded sample."""
+    import rwkv_cuda_b200 as R
+    from oracle import wkv_oracle as O
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(42)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+    ru = lambda lo, hi, *s: torch.rand(*s, device=dev, generator=g) * (hi - lo) + lo
+    bf = torch.bfloat16
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    extra = {}
+    if op == "wkv4":       # config 1: RWKV-4 fp32 B4 T256 C256
+        B, T, C = 4, 256, 256
+        name, dtype, tokens = f"wkv4 fwd+bwd fp32 B{B} T{T} C{C}", "f32", B * T
+        w, u = -torch.exp(ru(-4, 1, C)), ru(-1, 1, C)
+        k, v, gy = 0.5 * rn(B, T, C), rn(B, T, C), rn(B, T, C)
+        y, gk, gv = (torch.empty(B, T, C, device=dev) for _ in range(3))
+        gw, gu = torch.zeros(B, C, device=dev), torch.zeros(B, C, device=dev)
+        fwd = lambda: R.ops.wkv4_forward(B, T, C, w, u, k, v, y)
+        bwd = lambda: R.ops.wkv4_backward(B, T, C, w, u, k, v, gy, gw, gu, gk, gv)
+        bytes_f, bytes_b = 12 * B * T * C, 20 * B * T * C
+        bound, note = "hbm", "latency bound: 1024 independent recurrences of 256 dependent steps"
+
+        def cpu():
+            xs = [x.cpu().requires_grad_(True) for x in (torch.log(-w), u, k, v)]
+            O.wkv4(*xs).backward(gy.cpu())
+        cpu_tokens, cpu_sample = B * T, f"full config (B{B} T{T} C{C}), fp32 formula + autograd"
+    elif op == "timex":    # config 2: depthwise_conv1d fp32 B32 C768 T768
+        B, C, T = 32, 768, 768
+        name, dtype, tokens = f"depthwise_conv1d fwd+bwd fp32 B{B} C{C} T{T}", "f32", B * T
+        w, k, gy = rn(C, T) / T ** 0.5, rn(B, C, T), rn(B, C, T)
+        x, gk, gws = torch.empty(B, C, T, device=dev), torch.empty(B, C, T, device=dev), torch.empty(C, T, device=dev)
+        fwd = lambda: R.ops.timex_forward(w, k, x, 0.1, B, C, T)
+        bwd = lambda: R.ops.timex_backward_reduced(w, k, gy, gws, gk, B, C, T)
+        bytes_f, bytes_b = 4 * (2 * B * C * T + C * T), 4 * (3 * B * C * T + 2 * C * T)
+        flop_f, flop_b = B * C * T * (T + 1), 2 * B * C * T * (T + 1)
+        bound, note = "fp32", "FP32-pipe bound (T/2 FMA per loaded element); peak is the nominal CUDA-core figure"
+
+        def cpu():
+            wl, kl = w.cpu().requires_grad_(True), k.cpu().requires_grad_(True)
+            O.timex_conv(wl, kl, 0.1).backward(gy.cpu())
+        cpu_tokens, cpu_sample = B * T, "full config, grouped conv1d formula + autograd, fp32"
+    elif op == "wkv5":     # config 3: RWKV-5 bf16 B8 T4096 C4096 N64
+        B, T, H, N = 8, 4096, 64, 64
+        C = H * N
+        name, dtype, tokens = f"wkv5 fwd+bwd bf16 B{B} T{T} C{C} N{N}", "bf16", B * T
+        r, k, v = ((0.5 * rn(B, T, C)).to(bf) for _ in range(3))
+        gy = rn(B, T, C).to(bf)
+        wraw, u = ru(-6, -1, H, N).to(bf), ru(-1, 1, H, N).to(bf)
+        ew = -torch.exp(wraw.float())
+        eew = torch.exp(ew)
+        y, gr, gk, gv = (torch.empty(B, T, C, dtype=bf, device=dev) for _ in range(4))
+        gw, gu = torch.empty(B, C, dtype=bf, device=dev), torch.empty(B, C, dtype=bf, device=dev)
+        fwd = lambda: R.ops.wkv5_forward(B, T, C, H, r, k, v, eew, u, y)
+        bwd = lambda: R.ops.wkv5_backward(B, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu)
+        bytes_f, bytes_b = 8 * C * B * T, 14 * C * B * T
+        bound, note = "hbm", "general-shape (scalar fp32) kernel: FP32-pipe bound, HBM roof shown for reference"
+        Tc = 256
+
+        def cpu():
+            xs = [x[:1, :Tc].float().cpu().requires_grad_(True) for x in (r, k, v)] + [wraw.float().cpu().requires_grad_(True), u.float().cpu().requires_grad_(True)]
+            O.wkv5(*xs, H).backward(gy[:1, :Tc].float().cpu())
+        cpu_tokens, cpu_sample = Tc, f"B1 T{Tc} C{C} N{N} fp32 recurrent formula + autograd"
+    elif op == "wkv6state":  # config 4: RWKV-6 with fp32 state in/out, bf16, B16 T4096 C4096 N64
+        B, T, H, N = 16, 4096, 64, 64
+        C = H * N
+        name, dtype, tokens = f"wkv6state(_ex) fwd+bwd bf16 B{B} T{T} C{C} N{N}", "bf16", B * T
+        r, k, v = ((0.5 * rn(B, T, C)).to(bf) for _ in range(3))
+        gy = rn(B, T, C).to(bf)
+        wraw, u = (rn(B, T, C) - 5.0).to(bf), ru(-1, 1, H, N).to(bf)
+        s0, dsT = 0.1 * rn(B, H, N, N), rn(B, H, N, N)
+        y, gr, gk, gv, gw = (torch.empty(B, T, C, dtype=bf, device=dev) for _ in range(5))
+        gu = torch.empty(B, C, dtype=bf, device=dev)
+        sT, ds0 = torch.empty_like(s0), torch.empty_like(s0)
+        fwd = lambda: R.ops.wkv6state_forward_ex(B, T, C, H, r, k, v, wraw, u, s0, y, sT)
+        bwd = lambda: R.ops.wkv6state_backward_ex(B, T, C, H, r, k, v, wraw, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0)
+        st = 4 * B * H * N * N
+        bytes_f, bytes_b = 10 * C * B * T + 2 * st, 18 * C * B * T + 2 * st
+        bound, note = "hbm", "general-shape (scalar fp32) kernel: FP32-pipe bound, HBM roof shown for reference"
+        Tc = 256
+
+        def cpu():
+            xs = [x[:1, :Tc].float().cpu().requires_grad_(True) for x in (r, k, v, wraw)] + [u.float().cpu().requires_grad_(True), s0[:1].cpu().requires_grad_(True)]
+            yy, ss = O.wkv6(*xs[:5], H, s0=xs[5], return_state=True)
+            torch.autograd.backward([yy, ss], [gy[:1, :Tc].float().cpu(), dsT[:1].cpu()])
+        cpu_tokens, cpu_sample = Tc, f"B1 T{Tc} C{C} N{N} fp32 recurrent formula + autograd"
+    else:
+        raise SystemExit(f"unknown --op {op}")
+
+    with ClockSampler(0) as clocks:
+        fwd_ms, bwd_ms = _time_fb(fwd, bwd, args.steps, args.warmup)
+    peak, peak_src = hbm_peak()
+    ach = bytes_b / (bwd_ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": op + " backward", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+            "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": bytes_b,
+            "fwd": {"achieved": bytes_f / (fwd_ms * 1e-3) / 1e9, "frac": bytes_f / (fwd_ms * 1e-3) / 1e9 / peak}, "note": note}
+    if bound == "fp32":
+        tf = flop_b / (bwd_ms * 1e-3) / 1e12
+        roof.update({"bound": "fp32 (CUDA cores)", "achieved": tf, "peak": FP32_NOMINAL_TFLOPS, "unit": "TFLOP/s",
+                     "frac": tf / FP32_NOMINAL_TFLOPS, "peak_source": "nominal 148 SMs x 128 lanes x 2 x 1.965 GHz",
+                     "hbm_frac": ach / peak,
+                     "fwd": {"achieved": flop_f / (fwd_ms * 1e-3) / 1e12, "frac": flop_f / (fwd_ms * 1e-3) / 1e12 / FP32_NOMINAL_TFLOPS}})
+    out = {"metric": f"{op} fwd+bwd tokens/s", "value": tokens / ((fwd_ms + bwd_ms) * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True,
+           "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": name},
+           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, "gpu_launches": 2 * args.steps + (1 if op == "timex" else 0) * args.steps,
+           "clocks": clocks.summary()}
+    if not args.no_cpu_baseline:
+        ct = _cpu_time(cpu)
+        out["cpu_baseline"] = {"value": cpu_tokens / ct, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": cpu_sample}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -250,6 +395,8 @@ def main():
     ap.add_argument("--cpu-seq", type=int, default=256, help="sequence length of one CPU-baseline step (B=1, C=4096)")
     ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
     ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
+    ap.add_argument("--op", default="wkv7", choices=["wkv7", "wkv4", "timex", "wkv5", "wkv6state"],
+                    help="wkv7 = the headline configuration (default); the others are BASELINE configurations 1-4")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -262,6 +409,10 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
+    if args.op != "wkv7":
+        if rank == 0:
+            run_secondary(args.op, args)
+        return
     import torch.distributed as dist
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)

@@ -23,6 +23,7 @@ constexpr int NT = 128;   // threads per CTA: 4 warps, warp w owns state rows 16
 constexpr int PT = 72;    // pitch (floats) of token-major [16][64] operand arrays
 constexpr int PK = 68;    // pitch (floats) of token-major arrays that are read along the token index
 constexpr int PU = 24;    // pitch (floats) of the 16x16 matrices
+constexpr int RP = 72;    // pitch (bf16 elements) of the staged [16][64] input tiles in the backward kernels
 constexpr int PS = 68;    // pitch (floats) of the [16][64] output staging rows
 constexpr float kWScale = -0.6065306597126334f;  // -exp(-1/2)
 

@@ -25,7 +25,7 @@ namespace v7c {
 constexpr int PS0 = 68;  // pitch of the staged 64x64 state (read along its rows' index)
 
 struct BwdSmem {
-    static constexpr int kRawBytes = 2 * 7 * L * N * 2;              // bf16 [2][7][L*N]: r w k v a b dy
+    static constexpr int kRawBytes = 2 * 7 * L * RP * 2;             // bf16 [2][7][L*N]: r w k v a b dy
     static constexpr int kSa = kRawBytes / 4;                        // fp32 [L][PT]
     static constexpr int kS0 = kSa + L * PT;                         // fp32 [N][PS0]
     static constexpr int kAt = kS0 + N * PS0;                        // token-major, pitch PK, channels permuted:
@@ -89,7 +89,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     auto issue_raw = [&](int c, int stage) {
         const i64 off = tok0 + (i64)(c * L + lrow) * C + lseg * 8;
 #pragma unroll
-        for (int x = 0; x < 7; ++x) cp_async16(raw + ((stage * 7 + x) * L + lrow) * N + lseg * 8, src[x] + off);
+        for (int x = 0; x < 7; ++x) cp_async16(raw + ((stage * 7 + x) * L + lrow) * RP + lseg * 8, src[x] + off);
         cp_async_commit();
     };
     // sa (16 x 64 fp32) and the chunk-start state (64 x 64 fp32) are single-buffered: they are
@@ -116,13 +116,13 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         cp_async_wait<1>();   // this chunk's input tiles (the state group may still be in flight)
         __syncthreads();
         if (c > 0) issue_raw(c - 1, stage ^ 1); else cp_async_commit();
-        const bf16* R = raw + (stage * 7 + 0) * L * N;
-        const bf16* Wr = raw + (stage * 7 + 1) * L * N;
-        const bf16* K = raw + (stage * 7 + 2) * L * N;
-        const bf16* V = raw + (stage * 7 + 3) * L * N;
-        const bf16* A = raw + (stage * 7 + 4) * L * N;
-        const bf16* Bv = raw + (stage * 7 + 5) * L * N;
-        const bf16* DY = raw + (stage * 7 + 6) * L * N;
+        const bf16* R = raw + (stage * 7 + 0) * L * RP;
+        const bf16* Wr = raw + (stage * 7 + 1) * L * RP;
+        const bf16* K = raw + (stage * 7 + 2) * L * RP;
+        const bf16* V = raw + (stage * 7 + 3) * L * RP;
+        const bf16* A = raw + (stage * 7 + 4) * L * RP;
+        const bf16* Bv = raw + (stage * 7 + 5) * L * RP;
+        const bf16* DY = raw + (stage * 7 + 6) * L * RP;
         const float* SA = SAs;
         const float* S0 = S0s;
 
@@ -133,7 +133,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             float run = 0.f;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                const float x = to_f(Wr[(t0 + q) * N + j]);
+                const float x = to_f(Wr[(t0 + q) * RP + j]);
                 run += __fdividef(kWScale, 1.f + __expf(-x));
                 cs[q] = run;
             }
@@ -148,12 +148,12 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
                 const float wt = __expf(lam), iw = __expf(-lam);
-                At[tt * PK + jp] = tf32f(to_f(A[tt * N + j]) * wprev);
-                Rt[tt * PK + jp] = tf32f(to_f(R[tt * N + j]) * wt);
-                Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * N + j]) * iw);
-                Kt[tt * PK + jp] = tf32f(to_f(K[tt * N + j]) * iw);
-                Vf[tt * PK + jp] = to_f(V[tt * N + j]);
-                dYf[tt * PK + jp] = to_f(DY[tt * N + j]);
+                At[tt * PK + jp] = tf32f(to_f(A[tt * RP + j]) * wprev);
+                Rt[tt * PK + jp] = tf32f(to_f(R[tt * RP + j]) * wt);
+                Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * RP + j]) * iw);
+                Kt[tt * PK + jp] = tf32f(to_f(K[tt * RP + j]) * iw);
+                Vf[tt * PK + jp] = to_f(V[tt * RP + j]);
+                dYf[tt * PK + jp] = to_f(DY[tt * RP + j]);
                 Wt[tt * PK + j] = wt;
                 wprev = wt;
             }
@@ -295,8 +295,8 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
                 const float wu = Wt[u * PK + j], iwu = __frcp_rn(wu);
                 const float wp = u > 0 ? Wt[(u - 1) * PK + j] : 1.f;
-                const float xa = to_f(A[u * N + j]) * wp, xr = to_f(R[u * N + j]) * wu;
-                const float xb = to_f(Bv[u * N + j]) * iwu, xk = to_f(K[u * N + j]) * iwu;
+                const float xa = to_f(A[u * RP + j]) * wp, xr = to_f(R[u * RP + j]) * wu;
+                const float xb = to_f(Bv[u * RP + j]) * iwu, xk = to_f(K[u * RP + j]) * iwu;
                 atreg[ks][e] = tf32(xa); atlo[ks][e] = tf32(xa - __uint_as_float(atreg[ks][e]));
                 rtreg[ks][e] = tf32(xr); rtlo[ks][e] = tf32(xr - __uint_as_float(rtreg[ks][e]));
                 btreg[ks][e] = tf32(xb); btlo[ks][e] = tf32(xb - __uint_as_float(btreg[ks][e]));
@@ -345,13 +345,13 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const float wprev = tt > 0 ? Wt[(tt - 1) * PK + j] : 1.f;
                 const float dk = Z1[nt][e] * iw, db = Z1[2 + nt][e] * iw;
                 const float da = Z2[nt][e] * wprev, dr = Z2[2 + nt][e] * wt;
-                const float rr = to_f(R[tt * N + j]), aa = to_f(A[tt * N + j]);
-                const float bq = to_f(Bv[tt * N + j]), kq = to_f(K[tt * N + j]);
+                const float rr = to_f(R[tt * RP + j]), aa = to_f(A[tt * RP + j]);
+                const float bq = to_f(Bv[tt * RP + j]), kq = to_f(K[tt * RP + j]);
                 const i64 o = tok0 + (i64)(c * L + tt) * C + j;
                 store_bf16(dk_ + o, dk); store_bf16(db_ + o, db); store_bf16(da_ + o, da); store_bf16(dr_ + o, dr);
                 ada[nt][e] = aa * da;
                 cterm[nt][e] = rr * dr + ada[nt][e] - bq * db - kq * dk;
-                const float sg = 1.f / (1.f + __expf(-to_f(Wr[tt * N + j])));
+                const float sg = 1.f / (1.f + __expf(-to_f(Wr[tt * RP + j])));
                 sgd[nt][e] = kWScale * sg * (1.f - sg);
             }
         // exclusive prefix of cterm along the 16 tokens of each row: lanes t = 0..3 of a quad hold

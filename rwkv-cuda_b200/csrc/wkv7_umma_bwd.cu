@@ -24,7 +24,7 @@ constexpr int kColE = 0, kColET = 64, kColX2 = 128, kColZ1 = 160, kColUb = 192;
 __device__ int g_umma_bwd_error = 0;
 
 struct BSmem {
-    static constexpr int kRawBytes = 2 * 7 * L * N * 2;          // bf16 [2][7][L*N]: r w k v a b dy
+    static constexpr int kRawBytes = 2 * 7 * L * RP * 2;         // bf16 [2][7][L*N]: r w k v a b dy
     static constexpr int kARt = kRawBytes;                        // [A~;R~]  token-major, K = j
     static constexpr int kBKt = kARt + 16 * LBO_T;                // [B~;K~]  (read as 64 rows: runs on into VSt)
     static constexpr int kVSt = kBKt + 16 * LBO_T;                // [V;SA]   token-major, K = i
@@ -109,7 +109,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     auto issue_raw = [&](int c, int stage) {
         const i64 off = tok0 + (i64)(c * L + lrow) * C + lseg * 8;
 #pragma unroll
-        for (int x = 0; x < 7; ++x) cp_async16(raw + ((stage * 7 + x) * L + lrow) * N + lseg * 8, src[x] + off);
+        for (int x = 0; x < 7; ++x) cp_async16(raw + ((stage * 7 + x) * L + lrow) * RP + lseg * 8, src[x] + off);
         cp_async_commit();
     };
     // sa (16 tokens x 64 fp32) goes straight into rows 16..31 of the [V;SA] operand, 16 bytes a piece
@@ -133,13 +133,13 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         if (__syncthreads_or(fail)) break;
         tc_fence_after();
         if (c > 0) issue_raw(c - 1, stage ^ 1); else cp_async_commit();
-        const bf16* R = raw + (stage * 7 + 0) * L * N;
-        const bf16* Wr = raw + (stage * 7 + 1) * L * N;
-        const bf16* K = raw + (stage * 7 + 2) * L * N;
-        const bf16* V = raw + (stage * 7 + 3) * L * N;
-        const bf16* A = raw + (stage * 7 + 4) * L * N;
-        const bf16* Bv = raw + (stage * 7 + 5) * L * N;
-        const bf16* DY = raw + (stage * 7 + 6) * L * N;
+        const bf16* R = raw + (stage * 7 + 0) * L * RP;
+        const bf16* Wr = raw + (stage * 7 + 1) * L * RP;
+        const bf16* K = raw + (stage * 7 + 2) * L * RP;
+        const bf16* V = raw + (stage * 7 + 3) * L * RP;
+        const bf16* A = raw + (stage * 7 + 4) * L * RP;
+        const bf16* Bv = raw + (stage * 7 + 5) * L * RP;
+        const bf16* DY = raw + (stage * 7 + 6) * L * RP;
 
         // the 32 elements of the chunk-start state this thread needs: S0[i = 8ks+2t (+1)][j = row0+g (+8)]
         float s0f[8][4];
@@ -159,7 +159,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             float run = 0.f;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                const float x = to_f(Wr[(t0 + q) * N + j]);
+                const float x = to_f(Wr[(t0 + q) * RP + j]);
                 run += __fdividef(kWScale, 1.f + __expf(-x));
                 cs[q] = run;
             }
@@ -175,14 +175,14 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
                 const float wt = __expf(lam), iw = __expf(-lam);
-                at[q] = tf32f(to_f(A[tt * N + j]) * wprev);
-                rt[q] = tf32f(to_f(R[tt * N + j]) * wt);
-                dyv[q] = to_f(DY[tt * N + j]);
+                at[q] = tf32f(to_f(A[tt * RP + j]) * wprev);
+                rt[q] = tf32f(to_f(R[tt * RP + j]) * wt);
+                dyv[q] = to_f(DY[tt * RP + j]);
                 *reinterpret_cast<float*>(ARt + canon(tt, j, LBO_T)) = at[q];
                 *reinterpret_cast<float*>(ARt + canon(16 + tt, j, LBO_T)) = rt[q];
-                *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = tf32f(to_f(Bv[tt * N + j]) * iw);
-                *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = tf32f(to_f(K[tt * N + j]) * iw);
-                *reinterpret_cast<float*>(VSt + canon(tt, j, LBO_T)) = to_f(V[tt * N + j]);
+                *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = tf32f(to_f(Bv[tt * RP + j]) * iw);
+                *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = tf32f(to_f(K[tt * RP + j]) * iw);
+                *reinterpret_cast<float*>(VSt + canon(tt, j, LBO_T)) = to_f(V[tt * RP + j]);
                 dYf[tt * PK + jp] = dyv[q];
                 Wt[tt * PK + j] = wt;
                 wprev = wt;
@@ -395,7 +395,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
                     const float wu = Wt[u * PK + j];
                     const float wp = u > 0 ? Wt[(u - 1) * PK + j] : 1.f;
-                    const float xa = to_f(A[u * N + j]) * wp, xr = to_f(R[u * N + j]) * wu;
+                    const float xa = to_f(A[u * RP + j]) * wp, xr = to_f(R[u * RP + j]) * wu;
                     hi[ks][e] = tf32(xa); lo[ks][e] = tf32(xa - __uint_as_float(hi[ks][e]));
                     hi2[ks][e] = tf32(xr); lo2[ks][e] = tf32(xr - __uint_as_float(hi2[ks][e]));
                 }
@@ -409,7 +409,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int e = 0; e < 4; ++e) {
                     const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
                     const float iwu = __frcp_rn(Wt[u * PK + j]);
-                    const float xb = to_f(Bv[u * N + j]) * iwu, xk = to_f(K[u * N + j]) * iwu;
+                    const float xb = to_f(Bv[u * RP + j]) * iwu, xk = to_f(K[u * RP + j]) * iwu;
                     hi[ks][e] = tf32(xb); lo[ks][e] = tf32(xb - __uint_as_float(hi[ks][e]));
                     hi2[ks][e] = tf32(xk); lo2[ks][e] = tf32(xk - __uint_as_float(hi2[ks][e]));
                 }
@@ -452,13 +452,13 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const float wprev = tt > 0 ? Wt[(tt - 1) * PK + j] : 1.f;
                 const float dk = Z1[nt][e] * iw, db = Z1[2 + nt][e] * iw;
                 const float da = Z2[nt][e] * wprev, dr = Z2[2 + nt][e] * wt;
-                const float rr = to_f(R[tt * N + j]), aa = to_f(A[tt * N + j]);
-                const float bq = to_f(Bv[tt * N + j]), kq = to_f(K[tt * N + j]);
+                const float rr = to_f(R[tt * RP + j]), aa = to_f(A[tt * RP + j]);
+                const float bq = to_f(Bv[tt * RP + j]), kq = to_f(K[tt * RP + j]);
                 const i64 o = tok0 + (i64)(c * L + tt) * C + j;
                 store_bf16(dk_ + o, dk); store_bf16(db_ + o, db); store_bf16(da_ + o, da); store_bf16(dr_ + o, dr);
                 ada[nt][e] = aa * da;
                 cterm[nt][e] = rr * dr + ada[nt][e] - bq * db - kq * dk;
-                const float sg = 1.f / (1.f + __expf(-to_f(Wr[tt * N + j])));
+                const float sg = 1.f / (1.f + __expf(-to_f(Wr[tt * RP + j])));
                 sgd[nt][e] = kWScale * sg * (1.f - sg);
             }
 #pragma unroll
