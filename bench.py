@@ -105,21 +105,17 @@ class V7Workload:
     dram_bytes_per_token_bwd = (1.149444e9 + 0.385793e9) / (8 * 1024)
 
     def e2e_step(self):
-        """Host buffers in, host buffers out, through the public operator API."""
+        """Host buffers in, host buffers out, through the public host-buffer API
+        (rwkv_cuda_b200.host_pipeline): every operand starts in pinned host memory and every result
+        ends there; copies in both directions and the kernels are inside the timed region."""
         if self.host_out is None:
-            self.host_out = [torch.empty_like(self.host_in[0]).pin_memory() for _ in range(7)]
-            self.host_sout = [torch.empty_like(self.host_s0).pin_memory() for _ in range(2)]
-        for d, h in zip(self.inp, self.host_in):
-            d.copy_(h, non_blocking=True)
-        self.dy.copy_(self.host_dy, non_blocking=True)
-        self.s0.copy_(self.host_s0, non_blocking=True)
-        self.dsT.copy_(self.host_dsT, non_blocking=True)
-        self.forward()
-        self.backward()
-        for h, d in zip(self.host_out, [self.y] + self.grads):
-            h.copy_(d, non_blocking=True)
-        self.host_sout[0].copy_(self.sT, non_blocking=True)
-        self.host_sout[1].copy_(self.ds0, non_blocking=True)
+            names = self.R.host_pipeline.Wkv7HostPipeline
+            self.host_out = {n: torch.empty_like(self.host_in[0]).pin_memory() for n in names.OUT}
+            self.host_out.update(sT=torch.empty_like(self.host_s0).pin_memory(), ds0=torch.empty_like(self.host_s0).pin_memory())
+            self.host_named = dict(zip(("r", "w", "k", "v", "a", "b"), self.host_in))
+            self.host_named.update(dy=self.host_dy, s0=self.host_s0, dsT=self.host_dsT)
+            self.pipe = names(self.T, self.H, self.N, self.dev, slice_batch=min(2, self.b))
+        self.pipe.forward_backward(self.host_named, self.host_out)
 
     def e2e_bytes(self):
         big = self.host_in[0].numel() * 2

@@ -5,9 +5,10 @@ BlinkDL/RWKV-CUDA, behind that project's operator interface.
     load       stand-in for torch.utils.cpp_extension.load as the reference harnesses call it
     functions  torch.autograd.Function classes named as in the reference harnesses
     dist       batch sharding and the parameter-gradient all-reduce for multi-GPU runs
+    host_pipeline  RWKV-7 forward+backward on operands that live in pinned host memory (streamed in batch slices)
 """
-from . import _lib, ops, functions, dist  # noqa: F401
+from . import _lib, ops, functions, dist, host_pipeline  # noqa: F401
 from .load import load, parse_defines  # noqa: F401
 from ._lib import RwkvB200Error  # noqa: F401
 
-__all__ = ["ops", "functions", "dist", "load", "parse_defines", "RwkvB200Error"]
+__all__ = ["ops", "functions", "dist", "host_pipeline", "load", "parse_defines", "RwkvB200Error"]

@@ -26,6 +26,7 @@ int wkv7_umma_backward(int B, int T, int H, const void* r, const void* w, const 
                        const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,
                        cudaStream_t st);
 int wkv7_umma_bwd_error();
+
 int wkv7_chunked_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v,
                           const void* a, const void* b, const void* dy, const float* dsT, const float* s,
                           const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,

@@ -127,3 +127,30 @@ def test_functions_autograd_classes():
           lambda r, k, v, w, u: O.wkv6(r, k, v, w, u, H), (r, k, v, wt, uh))
     check("WKV_6STATE", lambda r, k, v, w, u, s: Fn.WKV_6STATE.apply(B, T, C, H, r, k, v, w, u, s),
           lambda r, k, v, w, u, s: O.wkv6(r, k, v, w, u, H, s0=s), (r, k, v, wt, uh, s))
+
+
+def test_host_pipeline_matches_resident_run():
+    """Operands in pinned host memory, streamed in batch slices: same bits as the resident run."""
+    import rwkv_cuda_b200 as R
+    B, T, H, N = 5, 64, 2, 64          # 5 rows in slices of 2: the last slice is ragged
+    bf = torch.bfloat16
+    inp = Hh.v7_inputs(B, T, H, N, seed=9)
+    host_in = {n: inp[n].to(bf).view(B, T, H, N).contiguous().pin_memory() for n in ("r", "w", "k", "v", "a", "b", "dy")}
+    host_in.update(s0=inp["s0"].contiguous().pin_memory(), dsT=inp["dsT"].contiguous().pin_memory())
+    host_out = {n: torch.empty(B, T, H, N, dtype=bf).pin_memory() for n in R.host_pipeline.Wkv7HostPipeline.OUT}
+    host_out.update(sT=torch.empty(B, H, N, N).pin_memory(), ds0=torch.empty(B, H, N, N).pin_memory())
+    pipe = R.host_pipeline.Wkv7HostPipeline(T, H, N, DEV, slice_batch=2)
+    for _ in range(2):                  # twice: the device buffer sets are reused
+        pipe.forward_backward(host_in, host_out)
+        pipe.synchronize()
+    d = {n: t.to(DEV) for n, t in host_in.items()}
+    y, sT, ds0 = torch.empty_like(d["r"]), torch.empty_like(d["s0"]), torch.empty_like(d["s0"])
+    s = torch.empty(B, H, T // 16, N, N, device=DEV)
+    sa = torch.empty(B, T, H, N, device=DEV)
+    R.ops.wkv7_forward(d["s0"], d["r"], d["w"], d["k"], d["v"], d["a"], d["b"], y, sT, s, sa)
+    g = [torch.empty_like(y) for _ in range(6)]
+    R.ops.wkv7_backward(d["r"], d["w"], d["k"], d["v"], d["a"], d["b"], d["dy"], d["dsT"], s, sa, ds0, *g)
+    torch.cuda.synchronize()
+    want = dict(y=y, sT=sT, ds0=ds0, **dict(zip(("dr", "dw", "dk", "dv", "da", "db"), g)))
+    for n, t in want.items():
+        assert torch.equal(host_out[n], t.cpu()), n
