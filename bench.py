@@ -100,9 +100,9 @@ class V7Workload:
 
     launches_per_step = 2
     # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel per token, from the ncu
-    # capture of the reduced case (profiles/wkv7_chunked_fwd_bwd_B8_T1024.md); traffic is
+    # capture of the reduced case (profiles/wkv7_default_path_tcgen05_fwd_mma_bwd_B8_T1024.md); traffic is
     # proportional to the token count
-    dram_bytes_per_token_bwd = (1.149444e9 + 0.385793e9) / (8 * 1024)
+    dram_bytes_per_token_bwd = (1.149506e9 + 0.387098e9) / (8 * 1024)
 
     def e2e_step(self):
         """Host buffers in, host buffers out, through the public host-buffer API
@@ -391,6 +391,8 @@ def main():
     ap.add_argument("--cpu-seq", type=int, default=256, help="sequence length of one CPU-baseline step (B=1, C=4096)")
     ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
     ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
+    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="RWKV-7 kernel family (rwkvb200_wkv7_select_path); 0 = automatic")
     ap.add_argument("--op", default="wkv7", choices=["wkv7", "wkv4", "timex", "wkv5", "wkv6state"],
                     help="wkv7 = the headline configuration (default); the others are BASELINE configurations 1-4")
     args = ap.parse_args()
@@ -422,6 +424,10 @@ def main():
     assert W.B % world == 0, f"batch {W.B} does not divide over {world} ranks"
     b_local = W.B // world
     wl = W(b_local, dev, rank)
+    if args.path:
+        from rwkv_cuda_b200 import _lib
+        _lib.call("rwkvb200_wkv7_select_path", args.path)
+        W.name += f" (kernel family {args.path})"
 
     def barrier():
         if world > 1:
