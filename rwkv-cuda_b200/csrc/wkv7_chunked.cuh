@@ -26,13 +26,27 @@ constexpr int PU = 24;    // pitch (floats) of the 16x16 matrices
 constexpr int RP = 72;    // pitch (bf16 elements) of the staged [16][64] input tiles in the backward kernels
 constexpr int PS = 68;    // pitch (floats) of the [16][64] output staging rows
 constexpr float kWScale = -0.6065306597126334f;  // -exp(-1/2)
+constexpr float kWScale2 = kWScale * 1.4426950408889634f;   // the same in log2 units: cumulative log-decays are kept base 2
 
-__device__ __forceinline__ uint32_t tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
+// Round to TF32 (nearest, ties away from zero: what cvt.rna.tf32.f32 does) with two integer
+// instructions.  The cvt form issues on the quarter-rate conversion pipe, which the four resident
+// CTAs of an SM hit at the same time during operand preparation.
+__device__ __forceinline__ uint32_t tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 __device__ __forceinline__ float tf32f(float x) { return __uint_as_float(tf32(x)); }
+
+// Single-instruction approximations (flush-to-zero forms: no denormal fix-up code around them).
+// Their arguments here are decays >= 6e-5, sums 1 + e^x and log-decays in [-10, 0].
+__device__ __forceinline__ float fex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fexp(float x) { return fex2(x * 1.4426950408889634f); }
+__device__ __forceinline__ float frcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // D += A(16x8, row) * B(8x8, col), TF32 in, fp32 accumulate.
 // A: a0=(g,t) a1=(g+8,t) a2=(g,t+4) a3=(g+8,t+4); B: b0=(k=t,n=g) b1=(k=t+4,n=g);
@@ -49,6 +63,22 @@ __device__ __forceinline__ void mma8(float (&d)[4], uint32_t a0, uint32_t a1, ui
 // first.  Reading positions (t, t+4) of such an array yields channels (2t, 2t+1), i.e. the
 // permuted k order, with plain 32-bit loads.
 __device__ __forceinline__ int perm8(int c) { return (c >> 1) + ((c & 1) << 2); }
+
+// Key-channel relabelling used by the backward kernel.  The algorithm is equivariant under a
+// permutation of the key index j applied to r, w, k, a, b, their gradients and the state columns,
+// so inside each block of 16 key channels the kernel works on "logical" indices
+//   logical = (real >> 1) + 8 * (real & 1)          real = 2 * (logical & 7) + (logical >> 3)
+// which makes the two fragment rows a thread owns (g, g+8) the adjacent real channels (2g, 2g+1):
+// every per-row access to the bf16 tiles, to W_t and to global memory is one 32- or 64-bit access.
+__device__ __forceinline__ int key_logical(int real) { return (real & ~15) + ((real & 15) >> 1) + ((real & 1) << 3); }
+__device__ __forceinline__ int key_real(int logical) { return (logical & ~15) + ((logical & 7) << 1) + ((logical >> 3) & 1); }
+__device__ __forceinline__ float2 bf16x2_to_f2(uint32_t x) {
+    return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
 
 // Throughout, the contraction index inside one k-step of 8 is permuted so that MMA slot t maps
 // to element 2t and slot t+4 to element 2t+1.  An accumulator tile (d0..d3) is then directly an
@@ -196,29 +226,101 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int K>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(K) : "memory"); }
 
-// T = (I - U)^-1 for a strictly upper triangular 16x16 U (U[s][m], pitch PU), by back
-// substitution in fp32; lane t (< 16) owns column t.  Result rounded to TF32 and stored
-// transposed (Tt[t][s]) or, with NATURAL, as T[s][t].  Called by one full warp.
+// Optional per-phase cycle counters (compile with -DRWKVB200_PHASE_CLOCKS; off in the shipped
+// library): lane 0 of every warp of CTA (0,0) adds the cycles since its previous mark to
+// g_phase_clocks[warp][phase].  Each translation unit that uses the marks has its own copy and
+// exports a reader next to its kernel.
+#ifdef RWKVB200_PHASE_CLOCKS
+static __device__ unsigned long long g_phase_clocks[4][16];
+#define WKV7_PHASE_BEGIN() long long phase_last_ = clock64()
+#define WKV7_PHASE(k)                                                                              \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {                       \
+            const long long now_ = clock64();                                                      \
+            atomicAdd(&g_phase_clocks[threadIdx.x >> 5][k], (unsigned long long)(now_ - phase_last_)); \
+            phase_last_ = now_;                                                                    \
+        }                                                                                          \
+    } while (0)
+#define WKV7_PHASE_READER(name)                                                                    \
+    extern "C" int name(unsigned long long* out64) {                                               \
+        return (int)cudaMemcpyFromSymbol(out64, g_phase_clocks, sizeof(g_phase_clocks));           \
+    }
+#else
+#define WKV7_PHASE_BEGIN()
+#define WKV7_PHASE(k)
+#define WKV7_PHASE_READER(name)
+#endif
+
+// T = (I - U)^-1 for a strictly upper triangular 16x16 U (U[s][m], pitch PU, fp32), in fp32, by one
+// full warp.  Blocked: with U = [U11 U12; 0 U22] (8x8 blocks), T = [T11  T11 U12 T22; 0  T22] and
+// T11, T22 the inverses of the diagonal blocks.  Lanes 0-7 (mirrored in 16-23) back-substitute the
+// columns of T11, lanes 8-15 (mirrored in 24-31) those of T22: 7 dependent steps instead of 15.  The
+// lane pair (8+t, 24+t) then forms column t of U12 T22 (four rows each, exchanged by shuffle) and of
+// T11 (U12 T22).  Result rounded to TF32 and stored transposed (Tt[t][s]) or, with NATURAL, as T[s][t].
 template <bool NATURAL = false>
 __device__ __forceinline__ void tri_inverse(const float* U, float* Tt, int lane) {
-    const int t = lane & 15;
-    float col[L];
+    const int blk = (lane >> 3) & 1, t = lane & 7, hi = lane >> 4, o = 8 * blk;
+    auto idx = [](int s, int c) { return NATURAL ? s * PU + c : c * PU + s; };
+    float col[8];
 #pragma unroll
-    for (int m = 0; m < L; ++m) col[m] = (m == t) ? 1.f : 0.f;
+    for (int m = 0; m < 8; ++m) col[m] = (m == t) ? 1.f : 0.f;
 #pragma unroll
-    for (int s = L - 2; s >= 0; --s) {
+    for (int s = 6; s >= 0; --s) {
         // T[s,t] = sum_{m>s} U[s,m] T[m,t]   (zero for s >= t because col[m>t] = 0)
+        const float4 u0 = *reinterpret_cast<const float4*>(U + (o + s) * PU + o);
+        const float4 u1 = *reinterpret_cast<const float4*>(U + (o + s) * PU + o + 4);
+        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
         float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-        for (int m = s + 1; m < L; ++m) {
-            if ((m - s) & 1) acc0 = fmaf(U[s * PU + m], col[m], acc0);
-            else acc1 = fmaf(U[s * PU + m], col[m], acc1);
+        for (int m = s + 1; m < 8; ++m) {
+            if ((m - s) & 1) acc0 = fmaf(u[m], col[m], acc0);
+            else acc1 = fmaf(u[m], col[m], acc1);
         }
         if (s < t) col[s] = acc0 + acc1;
     }
-    if (lane < 16) {
+    // T11 goes out unrounded for now (it is an operand below), T22 and the zero block are final
+    if (hi == 0) {
 #pragma unroll
-        for (int s = 0; s < L; ++s) Tt[NATURAL ? s * PU + t : t * PU + s] = tf32f(col[s]);
+        for (int s = 0; s < 8; ++s) Tt[idx(o + s, o + t)] = blk ? tf32f(col[s]) : col[s];
+    } else if (blk == 0) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) Tt[idx(8 + s, t)] = 0.f;
+    }
+    __syncwarp();
+    // column t of M = U12 T22: rows 4*hi .. 4*hi+3 in this lane, the other four from the mirror lane
+    float mv[4], mo[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float* ur = U + (4 * hi + q) * PU + 8;
+        const float4 u0 = *reinterpret_cast<const float4*>(ur), u1 = *reinterpret_cast<const float4*>(ur + 4);
+        mv[q] = fmaf(u0.x, col[0], fmaf(u0.y, col[1], fmaf(u0.z, col[2], u0.w * col[3]))) +
+                fmaf(u1.x, col[4], fmaf(u1.y, col[5], fmaf(u1.z, col[6], u1.w * col[7])));
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) mo[q] = __shfl_xor_sync(0xffffffffu, mv[q], 16);
+    if (blk == 1) {
+        float M[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            M[q] = hi ? mo[q] : mv[q];
+            M[4 + q] = hi ? mv[q] : mo[q];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {          // T12[s][t] = sum_m T11[s][m] M[m]  (T11 has its unit diagonal and zeros below it)
+            const int s = 4 * hi + q;
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < 8; m += 2) {
+                acc0 = fmaf(Tt[idx(s, m)], M[m], acc0);
+                acc1 = fmaf(Tt[idx(s, m + 1)], M[m + 1], acc1);
+            }
+            Tt[idx(s, 8 + t)] = tf32f(acc0 + acc1);
+        }
+    }
+    __syncwarp();
+    if (hi == 0 && blk == 0) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) Tt[idx(s, t)] = tf32f(col[s]);
     }
 }
 

@@ -16,6 +16,9 @@
 // (per key channel) and A0[j] = sum_i E_start[i,j] S0[i,j],
 //   dL/dlog d_t = A0 - sum_{tau<t} c_tau - a_t da_t
 // anchored afresh at every chunk so rounding does not accumulate along the sequence.
+// Key channels are handled under the relabelling of wkv7_chunked.cuh (key_logical / key_real):
+// E columns, ET rows and every [t][j] operand array are in logical order, W_t, the staged state and
+// the bf16 tiles in real order.
 #include "wkv7_chunked.cuh"
 #include "wkv7_dispatch.cuh"
 
@@ -81,8 +84,8 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int row = row0 + g + ((e & 2) ? 8 : 0), col = nt * 8 + 2 * t + (e & 1);
-            E[nt][e] = dsT_ ? dsT_[sbase + row * N + col] : 0.f;
-            ET[nt][e] = dsT_ ? dsT_[sbase + col * N + row] : 0.f;
+            E[nt][e] = dsT_ ? dsT_[sbase + row * N + key_real(col)] : 0.f;
+            ET[nt][e] = dsT_ ? dsT_[sbase + col * N + key_real(row)] : 0.f;
         }
 
     const int lrow = tid >> 3, lseg = tid & 7;
@@ -111,6 +114,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     issue_raw(nchunks - 1, (nchunks - 1) & 1);
     issue_state(nchunks - 1);
 
+    WKV7_PHASE_BEGIN();
     for (int c = nchunks - 1; c >= 0; --c) {
         const int stage = c & 1;
         cp_async_wait<1>();   // this chunk's input tiles (the state group may still be in flight)
@@ -126,6 +130,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         const float* SA = SAs;
         const float* S0 = S0s;
 
+        WKV7_PHASE(0);   // wait for input tiles
         // ---- prep -----------------------------------------------------------------------------
         {
             const int j = tid & 63, hf = tid >> 6, t0 = hf * 8;
@@ -134,32 +139,35 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const float x = to_f(Wr[(t0 + q) * RP + j]);
-                run += __fdividef(kWScale, 1.f + __expf(-x));
+                run = fmaf(kWScale2, frcp(1.f + fexp(-x)), run);
                 cs[q] = run;
             }
             Hs[hf * N + j] = run;
             __syncthreads();
             const float base = hf ? Hs[j] : 0.f;
-            if (hf == 0) We[j] = __expf(Hs[j] + Hs[N + j]);
-            float wprev = hf ? __expf(base) : 1.f;
-            const int jp = (j & ~7) + perm8(j & 7);
+            const int jl = key_logical(j);
+            if (hf == 0) We[jl] = fex2(Hs[j] + Hs[N + j]);
+            float wprev = hf ? fex2(base) : 1.f;
+            const int jp = (jl & ~7) + perm8(jl & 7);   // key-indexed arrays: logical order
+            const int ip = (j & ~7) + perm8(j & 7);     // value-indexed arrays (v, dy): natural order
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
-                const float wt = __expf(lam), iw = __expf(-lam);
+                const float wt = fex2(lam), iw = fex2(-lam);
                 At[tt * PK + jp] = tf32f(to_f(A[tt * RP + j]) * wprev);
                 Rt[tt * PK + jp] = tf32f(to_f(R[tt * RP + j]) * wt);
                 Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * RP + j]) * iw);
                 Kt[tt * PK + jp] = tf32f(to_f(K[tt * RP + j]) * iw);
-                Vf[tt * PK + jp] = to_f(V[tt * RP + j]);
-                dYf[tt * PK + jp] = to_f(DY[tt * RP + j]);
+                Vf[tt * PK + ip] = to_f(V[tt * RP + j]);
+                dYf[tt * PK + ip] = to_f(DY[tt * RP + j]);
                 Wt[tt * PK + j] = wt;
                 wprev = wt;
             }
         }
         __syncthreads();
 
+        WKV7_PHASE(1);   // prep
         // ---- small products: warp 0 U_ab (+T), 1 U_ak, 2 U_br, 3 U_kr; stored as [s][t] --------
         {
             const float* Am = (warp & 1) ? Kt : Bt;
@@ -185,6 +193,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
         }
 
+        WKV7_PHASE(2);   // U (+ inverse on warp 0)
         // ---- Ew = E diag(We), ETw = diag(We) ET;  X2 = Ew [B~ | K~]^T -------------------------
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
@@ -208,9 +217,11 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 mma8(X2[2 + nt], a0, a1, a2, a3, __float_as_uint(pk[0]), __float_as_uint(pk[4]));
             }
         }
+        WKV7_PHASE(3);   // scale E/ET, X2
         cp_async_wait<1>();   // sa and the chunk-start state have landed (only the next input tiles may be pending)
         __syncthreads();
 
+        WKV7_PHASE(4);   // barrier (inverse, sa, S0)
         // ---- EV and dV ------------------------------------------------------------------------
         {   // sa arrived as fp32: round it to TF32 once (it is only ever an MMA operand here)
             float4* p = reinterpret_cast<float4*>(SAs + lrow * PT + lseg * 8);
@@ -236,6 +247,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 store_bf16(dv_ + tok0 + (i64)(c * L + tt) * C + i, X2[2 + nt][e]);
                 EVs[tt * PK + (i & ~7) + perm8(i & 7)] = tf32f(EV[nt][e]);
             }
+        WKV7_PHASE(5);   // EV chain, dV
         __syncthreads();
 
         // ---- Gram blocks: warp 0 P1 = EV^T V, 1 P3 = EV^T SA, 2 P2 = dY^T V, 3 P4 = dY^T SA ----
@@ -262,13 +274,15 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     pt[tt * PU + u] = val;
                 }
         }
+        WKV7_PHASE(6);   // barrier + Gram
         // ---- Z1 = ETw [V | SA],  Z2 = S0^T [EV | dY]   (rows = key j) ---------------------------
         float Z1[4][4] = {}, Z2[4][4] = {};
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             const uint32_t a0 = tf32(ET[ks][0]), a1 = tf32(ET[ks][2]), a2 = tf32(ET[ks][1]), a3 = tf32(ET[ks][3]);
-            const float* p0 = S0 + (ks * 8 + 2 * t) * PS0 + row0 + g;   // A[m=j][k=i] = S0[i][j]
-            const uint32_t s0a = tf32(p0[0]), s1a = tf32(p0[8]), s2a = tf32(p0[PS0]), s3a = tf32(p0[PS0 + 8]);
+            const float* p0 = S0 + (ks * 8 + 2 * t) * PS0 + row0 + 2 * g;   // A[m=j][k=i] = S0[i][j], rows (g, g+8) = real (2g, 2g+1)
+            const float2 sx = *reinterpret_cast<const float2*>(p0), sy = *reinterpret_cast<const float2*>(p0 + PS0);
+            const uint32_t s0a = tf32(sx.x), s1a = tf32(sx.y), s2a = tf32(sy.x), s3a = tf32(sy.y);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const float* pv = Vf + (nt * 8 + g) * PK + ks * 8 + t;
@@ -281,6 +295,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 mma8(Z2[2 + nt], s0a, s1a, s2a, s3a, __float_as_uint(pd[0]), __float_as_uint(pd[4]));
             }
         }
+        WKV7_PHASE(7);   // Z1, Z2
         __syncthreads();
 
         // ---- dK' dB' (in Z1) and dA' dR' (in Z2) ------------------------------------------------
@@ -289,19 +304,32 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         uint32_t atreg[2][4], rtreg[2][4], btreg[2][4], ktreg[2][4];
         uint32_t atlo[2][4], rtlo[2][4], btlo[2][4], ktlo[2][4];
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks)
+        for (int ks = 0; ks < 2; ++ks) {
+            float2 wp2 = make_float2(1.f, 1.f);
+            if (ks > 0 || t > 0) wp2 = *reinterpret_cast<const float2*>(Wt + (ks * 8 + 2 * t - 1) * PK + row0 + 2 * g);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
-                const float wu = Wt[u * PK + j], iwu = __frcp_rn(wu);
-                const float wp = u > 0 ? Wt[(u - 1) * PK + j] : 1.f;
-                const float xa = to_f(A[u * RP + j]) * wp, xr = to_f(R[u * RP + j]) * wu;
-                const float xb = to_f(Bv[u * RP + j]) * iwu, xk = to_f(K[u * RP + j]) * iwu;
-                atreg[ks][e] = tf32(xa); atlo[ks][e] = tf32(xa - __uint_as_float(atreg[ks][e]));
-                rtreg[ks][e] = tf32(xr); rtlo[ks][e] = tf32(xr - __uint_as_float(rtreg[ks][e]));
-                btreg[ks][e] = tf32(xb); btlo[ks][e] = tf32(xb - __uint_as_float(btreg[ks][e]));
-                ktreg[ks][e] = tf32(xk); ktlo[ks][e] = tf32(xk - __uint_as_float(ktreg[ks][e]));
+            for (int uh = 0; uh < 2; ++uh) {      // fragment slots e = 2*uh (row g) and 2*uh+1 (row g+8) = real channels 2g, 2g+1
+                const int u = ks * 8 + 2 * t + uh, jr = row0 + 2 * g;
+                const float2 wu2 = *reinterpret_cast<const float2*>(Wt + u * PK + jr);
+                const float2 iw2 = make_float2(frcp(wu2.x), frcp(wu2.y));
+                const float2 a2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(A + u * RP + jr));
+                const float2 r2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(R + u * RP + jr));
+                const float2 b2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Bv + u * RP + jr));
+                const float2 k2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(K + u * RP + jr));
+                const float xa[2] = {a2.x * wp2.x, a2.y * wp2.y}, xr[2] = {r2.x * wu2.x, r2.y * wu2.y};
+                const float xb[2] = {b2.x * iw2.x, b2.y * iw2.y}, xk[2] = {k2.x * iw2.x, k2.y * iw2.y};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int e = 2 * uh + h;
+                    atreg[ks][e] = tf32(xa[h]); atlo[ks][e] = tf32(xa[h] - __uint_as_float(atreg[ks][e]));
+                    rtreg[ks][e] = tf32(xr[h]); rtlo[ks][e] = tf32(xr[h] - __uint_as_float(rtreg[ks][e]));
+                    btreg[ks][e] = tf32(xb[h]); btlo[ks][e] = tf32(xb[h] - __uint_as_float(btreg[ks][e]));
+                    ktreg[ks][e] = tf32(xk[h]); ktlo[ks][e] = tf32(xk[h] - __uint_as_float(ktreg[ks][e]));
+                }
+                wp2 = wu2;
             }
+        }
+        WKV7_PHASE(8);   // barrier + hi/lo loaders
         const float *P1n = Pn, *P2n = Pn + L * PU, *P3n = Pn + 2 * L * PU, *P4n = Pn + 3 * L * PU;
         const float *P1t = Ptr, *P2t = Ptr + L * PU, *P3t = Ptr + 2 * L * PU, *P4t = Ptr + 3 * L * PU;
         gemm_rs2<2, 2>(Z1, atreg, atlo, P1t, PU, g, t);      // dK' += A~^T P1 + R~^T P2  (B[k=u][n=t] = P[u][t])
@@ -313,20 +341,23 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         gemm_rs2<2, 2>(Z2 + 2, btreg, btlo, P4n, PU, g, t);  // dR'
         gemm_rs2<2, 2>(Z2 + 2, ktreg, ktlo, P2n, PU, g, t);
 
+        WKV7_PHASE(9);   // P products
         // ---- E and ET updates ------------------------------------------------------------------
         gemm_rs_kperm<8, 2>(E, evreg, At, PK, g, t);         // E += EV A~   (B[k=t][n=j] = a~_t[j])
         gemm_rs_kperm<8, 2>(E, dyreg, Rt, PK, g, t);         //    + dY R~
         gemm_rs_kperm<8, 2>(ET, atreg, EVs, PK, g, t);       // ET += A~^T EV^T (B[k=t][n=i] = e_t[i])
         gemm_rs_kperm<8, 2>(ET, rtreg, dYf, PK, g, t);       //     + R~^T dY^T
 
+        WKV7_PHASE(10);  // E, ET updates
         // ---- per-token gradients, rows j = row0+g (+8), columns = tokens --------------------------
         float A0[2] = {0.f, 0.f};                            // sum_i E_start[i,j] S0[i,j]
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = row0 + g + ((e & 2) ? 8 : 0), i = nt * 8 + 2 * t + (e & 1);
-                A0[e >> 1] = fmaf(ET[nt][e], S0[i * PS0 + j], A0[e >> 1]);
+            for (int q = 0; q < 2; ++q) {         // ET rows (g, g+8) = real key channels (2g, 2g+1)
+                const float2 sv = *reinterpret_cast<const float2*>(S0 + (nt * 8 + 2 * t + q) * PS0 + row0 + 2 * g);
+                A0[0] = fmaf(ET[nt][q], sv.x, A0[0]);
+                A0[1] = fmaf(ET[nt][2 + q], sv.y, A0[1]);
             }
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
@@ -335,27 +366,45 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
         __syncthreads();      // every warp is done with sa and the staged state
         if (c > 0) issue_state(c - 1); else cp_async_commit();
+        WKV7_PHASE(11);  // A0, barrier, state prefetch
         float cterm[2][4], ada[2][4], sgd[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                const float wt = Wt[tt * PK + j], iw = __frcp_rn(wt);
-                const float wprev = tt > 0 ? Wt[(tt - 1) * PK + j] : 1.f;
-                const float dk = Z1[nt][e] * iw, db = Z1[2 + nt][e] * iw;
-                const float da = Z2[nt][e] * wprev, dr = Z2[2 + nt][e] * wt;
-                const float rr = to_f(R[tt * RP + j]), aa = to_f(A[tt * RP + j]);
-                const float bq = to_f(Bv[tt * RP + j]), kq = to_f(K[tt * RP + j]);
-                const i64 o = tok0 + (i64)(c * L + tt) * C + j;
-                store_bf16(dk_ + o, dk); store_bf16(db_ + o, db); store_bf16(da_ + o, da); store_bf16(dr_ + o, dr);
-                ada[nt][e] = aa * da;
-                cterm[nt][e] = rr * dr + ada[nt][e] - bq * db - kq * dk;
-                const float sg = 1.f / (1.f + __expf(-to_f(Wr[tt * RP + j])));
-                sgd[nt][e] = kWScale * sg * (1.f - sg);
+            for (int q = 0; q < 2; ++q) {         // token tt, both rows of the thread: real channels jr, jr+1
+                const int tt = nt * 8 + 2 * t + q, jr = row0 + 2 * g;
+                const float2 wt = *reinterpret_cast<const float2*>(Wt + tt * PK + jr);
+                float2 wprev = make_float2(1.f, 1.f);
+                if (tt > 0) wprev = *reinterpret_cast<const float2*>(Wt + (tt - 1) * PK + jr);
+                const float2 rr = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(R + tt * RP + jr));
+                const float2 aa = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(A + tt * RP + jr));
+                const float2 bq = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Bv + tt * RP + jr));
+                const float2 kq = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(K + tt * RP + jr));
+                const float2 wr = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Wr + tt * RP + jr));
+                const float wtv[2] = {wt.x, wt.y}, wpv[2] = {wprev.x, wprev.y};
+                const float rv[2] = {rr.x, rr.y}, av[2] = {aa.x, aa.y}, bv2[2] = {bq.x, bq.y}, kv[2] = {kq.x, kq.y}, wv[2] = {wr.x, wr.y};
+                float dk[2], db[2], da[2], dr[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int e = 2 * h + q;
+                    const float iw = frcp(wtv[h]);
+                    dk[h] = Z1[nt][e] * iw; db[h] = Z1[2 + nt][e] * iw;
+                    da[h] = Z2[nt][e] * wpv[h]; dr[h] = Z2[2 + nt][e] * wtv[h];
+                    ada[nt][e] = av[h] * da[h];
+                    cterm[nt][e] = rv[h] * dr[h] + ada[nt][e] - bv2[h] * db[h] - kv[h] * dk[h];
+                    const float sg = frcp(1.f + fexp(-wv[h]));
+                    sgd[nt][e] = kWScale * sg * (1.f - sg);
+                }
+                const i64 o = tok0 + (i64)(c * L + tt) * C + jr;
+                *reinterpret_cast<uint32_t*>(dk_ + o) = f2_to_bf16x2(dk[0], dk[1]);
+                *reinterpret_cast<uint32_t*>(db_ + o) = f2_to_bf16x2(db[0], db[1]);
+                *reinterpret_cast<uint32_t*>(da_ + o) = f2_to_bf16x2(da[0], da[1]);
+                *reinterpret_cast<uint32_t*>(dr_ + o) = f2_to_bf16x2(dr[0], dr[1]);
             }
+        WKV7_PHASE(12);  // dk db da dr
         // exclusive prefix of cterm along the 16 tokens of each row: lanes t = 0..3 of a quad hold
         // tokens (2t, 2t+1) of tile 0 and (8+2t, 8+2t+1) of tile 1
+        float G[2][4];
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
             const int e0 = h2 * 2;
@@ -367,25 +416,33 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             if (t >= 2) { i0 += n0; i1 += n1; }
             const float tot0 = __shfl_sync(0xffffffffu, i0, 3, 4);
             const float ex0 = i0 - p0, ex1 = tot0 + i1 - p1;
-            const int j = row0 + g + h2 * 8;
             const float pre[4] = {ex0, ex0 + cterm[0][e0], ex1, ex1 + cterm[1][e0]};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const int nt = q >> 1, e = e0 + (q & 1), tt = nt * 8 + 2 * t + (q & 1);
-                const float G = A0[h2] - pre[q] - ada[nt][e];
-                store_bf16(dw_ + tok0 + (i64)(c * L + tt) * C + j, G * sgd[nt][e]);
+                const int nt = q >> 1, e = e0 + (q & 1);
+                G[h2][q] = (A0[h2] - pre[q] - ada[nt][e]) * sgd[nt][e];
             }
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int tt = (q >> 1) * 8 + 2 * t + (q & 1);
+            *reinterpret_cast<uint32_t*>(dw_ + tok0 + (i64)(c * L + tt) * C + row0 + 2 * g) = f2_to_bf16x2(G[0][q], G[1][q]);
+        }
+        WKV7_PHASE(13);  // dw
     }
 
     if (ds0_ != nullptr) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            *reinterpret_cast<float2*>(ds0_ + sbase + (row0 + g) * N + nt * 8 + 2 * t) = make_float2(E[nt][0], E[nt][1]);
-            *reinterpret_cast<float2*>(ds0_ + sbase + (row0 + g + 8) * N + nt * 8 + 2 * t) = make_float2(E[nt][2], E[nt][3]);
+        for (int m = 0; m < 4; ++m) {   // logical columns of tiles 2m, 2m+1 = real columns 16m + 4t .. 16m + 4t + 3
+            *reinterpret_cast<float4*>(ds0_ + sbase + (row0 + g) * N + 16 * m + 4 * t) =
+                make_float4(E[2 * m][0], E[2 * m + 1][0], E[2 * m][1], E[2 * m + 1][1]);
+            *reinterpret_cast<float4*>(ds0_ + sbase + (row0 + g + 8) * N + 16 * m + 4 * t) =
+                make_float4(E[2 * m][2], E[2 * m + 1][2], E[2 * m][3], E[2 * m + 1][3]);
         }
     }
 }
+
+WKV7_PHASE_READER(rwkvb200_phase_clocks_chunked_bwd)
 
 }  // namespace v7c
 

@@ -105,21 +105,21 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const float x = to_f(Wr[(t0 + q) * N + j]);
-                run += __fdividef(kWScale, 1.f + __expf(-x));  // log decay, cumulative within the half
+                run = fmaf(kWScale2, frcp(1.f + fexp(-x)), run);  // log decay, cumulative within the half
                 cs[q] = run;
             }
             Hs[hf * N + j] = run;
             __syncthreads();
             const float base = hf ? Hs[j] : 0.f;
             const float lam_e = Hs[j] + Hs[N + j];
-            if (hf == 0) We[j] = __expf(lam_e);
-            float wprev = hf ? __expf(base) : 1.f;
+            if (hf == 0) We[j] = fex2(lam_e);
+            float wprev = hf ? fex2(base) : 1.f;
             const int jp = (j & ~7) + perm8(j & 7);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
-                const float wt = __expf(lam), iw = __expf(-lam);
+                const float wt = fex2(lam), iw = fex2(-lam);
                 At[tt * PT + j] = tf32f(to_f(A[tt * N + j]) * wprev);
                 Rt[tt * PT + j] = tf32f(to_f(R[tt * N + j]) * wt);
                 Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * N + j]) * iw);

@@ -125,6 +125,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     issue_sa(nchunks - 1);
     int fail = 0;
 
+    WKV7_PHASE_BEGIN();
     for (int c = nchunks - 1; c >= 0; --c) {
         const int stage = c & 1;
         const uint32_t par = (nchunks - 1 - c) & 1;
@@ -141,6 +142,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         const bf16* Bv = raw + (stage * 7 + 5) * L * RP;
         const bf16* DY = raw + (stage * 7 + 6) * L * RP;
 
+        WKV7_PHASE(0);   // wait for input tiles
         // the 32 elements of the chunk-start state this thread needs: S0[i = 8ks+2t (+1)][j = row0+g (+8)]
         float s0f[8][4];
         {
@@ -160,21 +162,21 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const float x = to_f(Wr[(t0 + q) * RP + j]);
-                run += __fdividef(kWScale, 1.f + __expf(-x));
+                run = fmaf(kWScale2, frcp(1.f + fexp(-x)), run);
                 cs[q] = run;
             }
             Hs[hf * N + j] = run;
             __syncthreads();
             const float base = hf ? Hs[j] : 0.f;
-            if (hf == 0) We[j] = __expf(Hs[j] + Hs[N + j]);
-            float wprev = hf ? __expf(base) : 1.f;
+            if (hf == 0) We[j] = fex2(Hs[j] + Hs[N + j]);
+            float wprev = hf ? fex2(base) : 1.f;
             const int jp = (j & ~7) + perm8(j & 7);
             float at[8], rt[8], dyv[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
-                const float wt = __expf(lam), iw = __expf(-lam);
+                const float wt = fex2(lam), iw = fex2(-lam);
                 at[q] = tf32f(to_f(A[tt * RP + j]) * wprev);
                 rt[q] = tf32f(to_f(R[tt * RP + j]) * wt);
                 dyv[q] = to_f(DY[tt * RP + j]);
@@ -200,6 +202,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
         tc_fence_after();
 
+        WKV7_PHASE(1);   // prep + barrier
         // ---- U on the tensor core; meanwhile round sa and scale E, ET by We -----------------------
         if (tid == 0) {
             const uint32_t id32 = umma_idesc(32);
@@ -246,6 +249,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
         tc_fence_after();
 
+        WKV7_PHASE(2);   // sa rounding, E/ET scaling, barrier
         // ---- X2 = Ew [B~|K~]^T and Z1 = ETw [V|SA] on the tensor core -----------------------------
         if (tid == 0) {
             const uint32_t id32 = umma_idesc(32);
@@ -279,6 +283,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 tri_inverse<true>(Uab, Tn, lane);
             }
         }
+        WKV7_PHASE(3);   // U wait, extraction, inverse
         if (!mbar_wait(bar + 1, par)) fail = 2;
         tc_fence_after();
         float X2[4][4];
@@ -289,6 +294,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
         tc_fence_after();
 
+        WKV7_PHASE(4);   // X2 wait, barrier
         // ---- EV and dV (mma.sync, registers) --------------------------------------------------------
         uint32_t dyreg[2][4], xreg[2][4], evreg[2][4];
 #pragma unroll
@@ -323,6 +329,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
         tc_fence_after();
 
+        WKV7_PHASE(5);   // EV chain, dV, barrier
         // ---- E += [EV|dY][A~;R~],  ET += [A~;R~]^T [EV|dY]^T on the tensor core -------------------
         if (tid == 0) {
             const uint32_t id64 = umma_idesc(64);
@@ -365,6 +372,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     pt[tt * PU + u] = val;
                 }
         }
+        WKV7_PHASE(6);   // Gram
         // ---- Z1 from tensor memory;  Z2 = S0^T [EV | dY]  (rows = key j) --------------------------
         float Z1[4][4], Z2[4][4] = {};
 #pragma unroll
@@ -383,6 +391,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         tmem_wait_ld();
         __syncthreads();
 
+        WKV7_PHASE(7);   // Z2, barrier
         // ---- dK' dB' (in Z1) and dA' dR' (in Z2): scaled vectors as hi + lo TF32 pairs ---------------
         {
             uint32_t hi[2][4], lo[2][4], hi2[2][4], lo2[2][4];
@@ -408,7 +417,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
-                    const float iwu = __frcp_rn(Wt[u * PK + j]);
+                    const float iwu = frcp(Wt[u * PK + j]);
                     const float xb = to_f(Bv[u * RP + j]) * iwu, xk = to_f(K[u * RP + j]) * iwu;
                     hi[ks][e] = tf32(xb); lo[ks][e] = tf32(xb - __uint_as_float(hi[ks][e]));
                     hi2[ks][e] = tf32(xk); lo2[ks][e] = tf32(xk - __uint_as_float(hi2[ks][e]));
@@ -419,6 +428,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             gemm_rs2<2, 2>(Z2 + 2, hi2, lo2, P2n, PU, g, t);
         }
 
+        WKV7_PHASE(8);   // hi/lo loaders + P products
         // ---- anchor of the decay gradient: A0[j] = sum_i ET_start[j,i] S0[i,j] ------------------------
         if (!mbar_wait(bar + 2, par)) fail = 3;
         tc_fence_after();
@@ -441,6 +451,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
         if (c > 0) issue_sa(c - 1); else cp_async_commit();   // every reader of this chunk's sa is done
 
+        WKV7_PHASE(9);   // wait E/ET update, A0
         // ---- per-token gradients, rows j = row0+g (+8), columns = tokens --------------------------
         float cterm[2][4], ada[2][4], sgd[2][4];
 #pragma unroll
@@ -448,7 +459,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                const float wt = Wt[tt * PK + j], iw = __frcp_rn(wt);
+                const float wt = Wt[tt * PK + j], iw = frcp(wt);
                 const float wprev = tt > 0 ? Wt[(tt - 1) * PK + j] : 1.f;
                 const float dk = Z1[nt][e] * iw, db = Z1[2 + nt][e] * iw;
                 const float da = Z2[nt][e] * wprev, dr = Z2[2 + nt][e] * wt;
@@ -458,7 +469,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 store_bf16(dk_ + o, dk); store_bf16(db_ + o, db); store_bf16(da_ + o, da); store_bf16(dr_ + o, dr);
                 ada[nt][e] = aa * da;
                 cterm[nt][e] = rr * dr + ada[nt][e] - bq * db - kq * dk;
-                const float sg = 1.f / (1.f + __expf(-to_f(Wr[tt * RP + j])));
+                const float sg = frcp(1.f + fexp(-to_f(Wr[tt * RP + j])));
                 sgd[nt][e] = kWScale * sg * (1.f - sg);
             }
 #pragma unroll
@@ -481,6 +492,7 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 store_bf16(dw_ + tok0 + (i64)(c * L + tt) * C + j, G * sgd[nt][e]);
             }
         }
+        WKV7_PHASE(10);  // per-token gradients
     }
 
     if (!fail && ds0_ != nullptr) {
@@ -499,6 +511,8 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kBwdTmemCols) : "memory");
 }
+
+WKV7_PHASE_READER(rwkvb200_phase_clocks_umma_bwd)
 
 }  // namespace v7u
 

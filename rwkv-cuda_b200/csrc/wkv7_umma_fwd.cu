@@ -117,6 +117,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     issue_loads(0);
     int fail = 0;
 
+    WKV7_PHASE_BEGIN();
     for (int c = 0; c < nchunks; ++c) {
         const uint32_t par = c & 1;
         cp_async_wait<0>();
@@ -130,6 +131,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         const bf16* A = raw + 4 * L * N;
         const bf16* Bv = raw + 5 * L * N;
 
+        WKV7_PHASE(0);   // wait for input tiles
         // ---- prep: thread = (channel j, half of the chunk) ------------------------------------
         {
             const int j = tid & 63, hf = tid >> 6, t0 = hf * 8;
@@ -138,20 +140,22 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const float x = to_f(Wr[(t0 + q) * N + j]);
-                run += __fdividef(kWScale, 1.f + __expf(-x));
+                run = fmaf(kWScale2, frcp(1.f + fexp(-x)), run);
                 cs[q] = run;
             }
+            WKV7_PHASE(8);   // prep: log-decays of the half chunk
             Hs[hf * N + j] = run;
             __syncthreads();
+            WKV7_PHASE(9);   // prep: exchange barrier
             const float base = hf ? Hs[j] : 0.f;
-            if (hf == 0) We[j] = __expf(Hs[j] + Hs[N + j]);
-            float wprev = hf ? __expf(base) : 1.f;
+            if (hf == 0) We[j] = fex2(Hs[j] + Hs[N + j]);
+            float wprev = hf ? fex2(base) : 1.f;
             float bt[8], kt[8], vv[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 const int tt = t0 + q;
                 const float lam = base + cs[q];
-                const float wt = __expf(lam), iw = __expf(-lam);
+                const float wt = fex2(lam), iw = fex2(-lam);
                 bt[q] = tf32f(to_f(Bv[tt * N + j]) * iw);
                 kt[q] = tf32f(to_f(K[tt * N + j]) * iw);
                 vv[q] = to_f(V[tt * N + j]);
@@ -169,12 +173,14 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
                 *reinterpret_cast<float4*>(SAV + canon(j, 16 + t0 + 4 * q4, LBO_C)) = make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]);
             }
         }
+        WKV7_PHASE(10);  // prep: scaled operands
         proxy_fence();
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
         if (c + 1 < nchunks) issue_loads(c + 1);   // the input tiles have been consumed: refill them now
 
+        WKV7_PHASE(1);   // prep + barrier
         // ---- U = [B~;K~][A~|R~]^T and X = S [A~|R~]^T on the tensor core ------------------------
         if (tid == 0) {
             const uint32_t id32 = umma_idesc(32);
@@ -189,6 +195,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         if (!mbar_wait(bar, par)) fail = 1;
         tc_fence_after();
 
+        WKV7_PHASE(2);   // U, X on the tensor core
         float X[4][4];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) tmem_ld8(X[nt], tw + kColX + nt * 8);
@@ -218,6 +225,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         __syncthreads();
         tc_fence_after();
 
+        WKV7_PHASE(3);   // U extraction, inverse, barrier
         // ---- the small chain on mma.sync, in registers --------------------------------------------
         uint32_t vreg[2][4], xreg[2][4], sareg[2][4];
 #pragma unroll
@@ -254,6 +262,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         __syncthreads();
         tc_fence_after();
 
+        WKV7_PHASE(4);   // chain, staging, barrier
         // ---- S += [SA|V] [B~;K~] on the tensor core ---------------------------------------------
         if (tid == 0) {
             const uint32_t id64 = umma_idesc(64);
@@ -279,9 +288,11 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
                 d[1] = *reinterpret_cast<const float4*>(sastage + lrow * PS + lseg * 8 + 4);
             }
         }
+        WKV7_PHASE(5);   // y, sa stores
         if (!mbar_wait(bar + 1, par)) fail = 2;
         tc_fence_after();
 
+        WKV7_PHASE(6);   // wait for the state update
         // ---- S <- S diag(We); this is the start state of the next chunk ---------------------------
         float* dst = (c + 1 < nchunks) ? (ck ? ck + (i64)(c + 1) * N * N : nullptr) : (sT_ ? sT_ + sbase : nullptr);
         float Sd[8][4];
@@ -299,6 +310,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             }
         }
         tmem_wait_st();
+        WKV7_PHASE(7);   // decay scaling + checkpoint
     }
 
     if (fail && tid == 0) atomicMax(&g_umma_error, fail);
@@ -306,6 +318,8 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
 }
+
+WKV7_PHASE_READER(rwkvb200_phase_clocks_umma_fwd)
 
 }  // namespace v7u
 
