@@ -142,6 +142,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 run = fmaf(kWScale2, frcp(1.f + fexp(-x)), run);
                 cs[q] = run;
             }
+            WKV7_PHASE(14);  // prep: log-decays of the half chunk
             Hs[hf * N + j] = run;
             __syncthreads();
             const float base = hf ? Hs[j] : 0.f;
@@ -150,21 +151,35 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             float wprev = hf ? fex2(base) : 1.f;
             const int jp = (jl & ~7) + perm8(jl & 7);   // key-indexed arrays: logical order
             const int ip = (j & ~7) + perm8(j & 7);     // value-indexed arrays (v, dy): natural order
+            // All loads of a batch of four tokens come before its stores: the staged tiles and the
+            // operand arrays live in the same shared-memory block, so the compiler keeps every load
+            // behind the stores that precede it in program order.
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int tt = t0 + q;
-                const float lam = base + cs[q];
-                const float wt = fex2(lam), iw = fex2(-lam);
-                At[tt * PK + jp] = tf32f(to_f(A[tt * RP + j]) * wprev);
-                Rt[tt * PK + jp] = tf32f(to_f(R[tt * RP + j]) * wt);
-                Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * RP + j]) * iw);
-                Kt[tt * PK + jp] = tf32f(to_f(K[tt * RP + j]) * iw);
-                Vf[tt * PK + ip] = to_f(V[tt * RP + j]);
-                dYf[tt * PK + ip] = to_f(DY[tt * RP + j]);
-                Wt[tt * PK + j] = wt;
-                wprev = wt;
+            for (int hb = 0; hb < 2; ++hb) {
+                float xa[4], xr[4], xb[4], xk[4], xv[4], xd[4], wt[4], iw[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q;
+                    xa[q] = to_f(A[tt * RP + j]); xr[q] = to_f(R[tt * RP + j]); xb[q] = to_f(Bv[tt * RP + j]);
+                    xk[q] = to_f(K[tt * RP + j]); xv[q] = to_f(V[tt * RP + j]); xd[q] = to_f(DY[tt * RP + j]);
+                    const float lam = base + cs[4 * hb + q];
+                    wt[q] = fex2(lam); iw[q] = fex2(-lam);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q;
+                    At[tt * PK + jp] = tf32f(xa[q] * wprev);
+                    Rt[tt * PK + jp] = tf32f(xr[q] * wt[q]);
+                    Bt[tt * PK + jp] = tf32f(xb[q] * iw[q]);
+                    Kt[tt * PK + jp] = tf32f(xk[q] * iw[q]);
+                    Vf[tt * PK + ip] = xv[q];
+                    dYf[tt * PK + ip] = xd[q];
+                    Wt[tt * PK + j] = wt[q];
+                    wprev = wt[q];
+                }
             }
         }
+        WKV7_PHASE(15);  // prep: exchange barrier, scaled operands
         __syncthreads();
 
         WKV7_PHASE(1);   // prep
@@ -251,28 +266,14 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
 
         // ---- Gram blocks: warp 0 P1 = EV^T V, 1 P3 = EV^T SA, 2 P2 = dY^T V, 3 P4 = dY^T SA ----
+        float P[2][4] = {};
         {
             const float* Am = (warp & 2) ? dYf : EVs;
             const float* Bm = (warp & 1) ? SA : Vf;
             uint32_t areg[8][4];
             load_a_plain<8>(areg, Am, PK, 0, g, t);
-            float P[2][4] = {};
             if (warp & 1) gemm_rs<2, 8>(P, areg, Bm, PT, g, t);        // sa: natural order, 64-bit reads
             else gemm_rs_plain<2, 8>(P, areg, Bm, PK, g, t);
-            const int which = (warp == 0) ? 0 : (warp == 2) ? 1 : (warp == 1) ? 2 : 3;  // P1 P2 P3 P4
-            const bool strict = !(warp & 2);
-            float* pn = Pn + which * L * PU;
-            float* pt = Ptr + which * L * PU;
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int u = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                    const bool keep = strict ? (u > tt) : (u >= tt);
-                    const float val = tf32f(keep ? P[nt][e] : 0.f);
-                    pn[u * PU + tt] = val;
-                    pt[tt * PU + u] = val;
-                }
         }
         WKV7_PHASE(6);   // barrier + Gram
         // ---- Z1 = ETw [V | SA],  Z2 = S0^T [EV | dY]   (rows = key j) ---------------------------
@@ -296,6 +297,22 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
         }
         WKV7_PHASE(7);   // Z1, Z2
+        {   // the Gram blocks go to shared memory only now: stores placed earlier would hold back the loads of Z1/Z2 above
+            const int which = (warp == 0) ? 0 : (warp == 2) ? 1 : (warp == 1) ? 2 : 3;  // P1 P2 P3 P4
+            const bool strict = !(warp & 2);
+            float* pn = Pn + which * L * PU;
+            float* pt = Ptr + which * L * PU;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int u = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
+                    const bool keep = strict ? (u > tt) : (u >= tt);
+                    const float val = tf32f(keep ? P[nt][e] : 0.f);
+                    pn[u * PU + tt] = val;
+                    pt[tt * PU + u] = val;
+                }
+        }
         __syncthreads();
 
         // ---- dK' dB' (in Z1) and dA' dR' (in Z2) ------------------------------------------------

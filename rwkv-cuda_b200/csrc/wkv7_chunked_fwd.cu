@@ -115,17 +115,29 @@ wkv7c_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             if (hf == 0) We[j] = fex2(lam_e);
             float wprev = hf ? fex2(base) : 1.f;
             const int jp = (j & ~7) + perm8(j & 7);
+            // loads of a batch of four tokens before its stores (tiles and operand arrays share one
+            // shared-memory block: the compiler keeps a load behind every earlier store)
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int tt = t0 + q;
-                const float lam = base + cs[q];
-                const float wt = fex2(lam), iw = fex2(-lam);
-                At[tt * PT + j] = tf32f(to_f(A[tt * N + j]) * wprev);
-                Rt[tt * PT + j] = tf32f(to_f(R[tt * N + j]) * wt);
-                Bt[tt * PK + jp] = tf32f(to_f(Bv[tt * N + j]) * iw);
-                Kt[tt * PK + jp] = tf32f(to_f(K[tt * N + j]) * iw);
-                Vf[tt * PK + j] = to_f(V[tt * N + j]);
-                wprev = wt;
+            for (int hb = 0; hb < 2; ++hb) {
+                float xa[4], xr[4], xb[4], xk[4], xv[4], wt[4], iw[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q;
+                    xa[q] = to_f(A[tt * N + j]); xr[q] = to_f(R[tt * N + j]); xb[q] = to_f(Bv[tt * N + j]);
+                    xk[q] = to_f(K[tt * N + j]); xv[q] = to_f(V[tt * N + j]);
+                    const float lam = base + cs[4 * hb + q];
+                    wt[q] = fex2(lam); iw[q] = fex2(-lam);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q;
+                    At[tt * PT + j] = tf32f(xa[q] * wprev);
+                    Rt[tt * PT + j] = tf32f(xr[q] * wt[q]);
+                    Bt[tt * PK + jp] = tf32f(xb[q] * iw[q]);
+                    Kt[tt * PK + jp] = tf32f(xk[q] * iw[q]);
+                    Vf[tt * PK + j] = xv[q];
+                    wprev = wt[q];
+                }
             }
         }
         __syncthreads();

@@ -172,22 +172,36 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             float wprev = hf ? fex2(base) : 1.f;
             const int jp = (j & ~7) + perm8(j & 7);
             float at[8], rt[8], dyv[8];
+            // loads of a batch of four tokens before its stores (tiles and operand arrays share one
+            // shared-memory block: the compiler keeps a load behind every earlier store)
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int tt = t0 + q;
-                const float lam = base + cs[q];
-                const float wt = fex2(lam), iw = fex2(-lam);
-                at[q] = tf32f(to_f(A[tt * RP + j]) * wprev);
-                rt[q] = tf32f(to_f(R[tt * RP + j]) * wt);
-                dyv[q] = to_f(DY[tt * RP + j]);
-                *reinterpret_cast<float*>(ARt + canon(tt, j, LBO_T)) = at[q];
-                *reinterpret_cast<float*>(ARt + canon(16 + tt, j, LBO_T)) = rt[q];
-                *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = tf32f(to_f(Bv[tt * RP + j]) * iw);
-                *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = tf32f(to_f(K[tt * RP + j]) * iw);
-                *reinterpret_cast<float*>(VSt + canon(tt, j, LBO_T)) = to_f(V[tt * RP + j]);
-                dYf[tt * PK + jp] = dyv[q];
-                Wt[tt * PK + j] = wt;
-                wprev = wt;
+            for (int hb = 0; hb < 2; ++hb) {
+                float xb[4], xk[4], xv[4], wt[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q, qq = 4 * hb + q;
+                    const float lam = base + cs[qq];
+                    wt[q] = fex2(lam);
+                    const float iw = fex2(-lam);
+                    at[qq] = tf32f(to_f(A[tt * RP + j]) * wprev);
+                    rt[qq] = tf32f(to_f(R[tt * RP + j]) * wt[q]);
+                    dyv[qq] = to_f(DY[tt * RP + j]);
+                    xb[q] = tf32f(to_f(Bv[tt * RP + j]) * iw);
+                    xk[q] = tf32f(to_f(K[tt * RP + j]) * iw);
+                    xv[q] = to_f(V[tt * RP + j]);
+                    wprev = wt[q];
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q, qq = 4 * hb + q;
+                    *reinterpret_cast<float*>(ARt + canon(tt, j, LBO_T)) = at[qq];
+                    *reinterpret_cast<float*>(ARt + canon(16 + tt, j, LBO_T)) = rt[qq];
+                    *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = xb[q];
+                    *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = xk[q];
+                    *reinterpret_cast<float*>(VSt + canon(tt, j, LBO_T)) = xv[q];
+                    dYf[tt * PK + jp] = dyv[qq];
+                    Wt[tt * PK + j] = wt[q];
+                }
             }
 #pragma unroll
             for (int q4 = 0; q4 < 2; ++q4) {
@@ -344,32 +358,18 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
 
         // ---- Gram blocks: warp 0 P1 = EV^T V, 1 P3 = EV^T SA, 2 P2 = dY^T V, 3 P4 = dY^T SA ----
+        float P[2][4] = {};
         {
             const float* Am = (warp & 2) ? dYf : EVs;
             const int brow = (warp & 1) ? 16 : 0;            // rows of [V;SA]
             uint32_t areg[8][4];
             load_a_plain<8>(areg, Am, PK, 0, g, t);
-            float P[2][4] = {};
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     const uint2 b2 = *reinterpret_cast<const uint2*>(VSt + canon(brow + nt * 8 + g, ks * 8 + 2 * t, LBO_T));
                     mma8(P[nt], areg[ks][0], areg[ks][1], areg[ks][2], areg[ks][3], b2.x, b2.y);
-                }
-            const int which = (warp == 0) ? 0 : (warp == 2) ? 1 : (warp == 1) ? 2 : 3;  // P1 P2 P3 P4
-            const bool strict = !(warp & 2);
-            float* pn = Pn + which * L * PU;
-            float* pt = Ptr + which * L * PU;
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int u = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                    const bool keep = strict ? (u > tt) : (u >= tt);
-                    const float val = tf32f(keep ? P[nt][e] : 0.f);
-                    pn[u * PU + tt] = val;
-                    pt[tt * PU + u] = val;
                 }
         }
         WKV7_PHASE(6);   // Gram
@@ -389,6 +389,22 @@ wkv7u_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
         }
         tmem_wait_ld();
+        {   // the Gram blocks go to shared memory only now: stores placed earlier would hold back the loads of Z1/Z2 above
+            const int which = (warp == 0) ? 0 : (warp == 2) ? 1 : (warp == 1) ? 2 : 3;  // P1 P2 P3 P4
+            const bool strict = !(warp & 2);
+            float* pn = Pn + which * L * PU;
+            float* pt = Ptr + which * L * PU;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int u = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
+                    const bool keep = strict ? (u > tt) : (u >= tt);
+                    const float val = tf32f(keep ? P[nt][e] : 0.f);
+                    pn[u * PU + tt] = val;
+                    pt[tt * PU + u] = val;
+                }
+        }
         __syncthreads();
 
         WKV7_PHASE(7);   // Z2, barrier

@@ -151,19 +151,31 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             if (hf == 0) We[j] = fex2(Hs[j] + Hs[N + j]);
             float wprev = hf ? fex2(base) : 1.f;
             float bt[8], kt[8], vv[8];
+            // loads of a batch of four tokens before its stores (tiles and operand arrays share one
+            // shared-memory block: the compiler keeps a load behind every earlier store)
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int tt = t0 + q;
-                const float lam = base + cs[q];
-                const float wt = fex2(lam), iw = fex2(-lam);
-                bt[q] = tf32f(to_f(Bv[tt * N + j]) * iw);
-                kt[q] = tf32f(to_f(K[tt * N + j]) * iw);
-                vv[q] = to_f(V[tt * N + j]);
-                *reinterpret_cast<float*>(ARt + canon(tt, j, LBO_T)) = tf32f(to_f(A[tt * N + j]) * wprev);
-                *reinterpret_cast<float*>(ARt + canon(16 + tt, j, LBO_T)) = tf32f(to_f(R[tt * N + j]) * wt);
-                *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = bt[q];
-                *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = kt[q];
-                wprev = wt;
+            for (int hb = 0; hb < 2; ++hb) {
+                float xa[4], xr[4], wt[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q, qq = 4 * hb + q;
+                    xa[q] = to_f(A[tt * N + j]); xr[q] = to_f(R[tt * N + j]);
+                    const float lam = base + cs[qq];
+                    wt[q] = fex2(lam);
+                    const float iw = fex2(-lam);
+                    bt[qq] = tf32f(to_f(Bv[tt * N + j]) * iw);
+                    kt[qq] = tf32f(to_f(K[tt * N + j]) * iw);
+                    vv[qq] = to_f(V[tt * N + j]);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int tt = t0 + 4 * hb + q, qq = 4 * hb + q;
+                    *reinterpret_cast<float*>(ARt + canon(tt, j, LBO_T)) = tf32f(xa[q] * wprev);
+                    *reinterpret_cast<float*>(ARt + canon(16 + tt, j, LBO_T)) = tf32f(xr[q] * wt[q]);
+                    *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = bt[qq];
+                    *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = kt[qq];
+                    wprev = wt[q];
+                }
             }
             // by channel: row j, K index = token (b~: 0..15, k~: 16..31; v: 16..31 of SAV)
 #pragma unroll
