@@ -251,76 +251,55 @@ static __device__ unsigned long long g_phase_clocks[4][16];
 #define WKV7_PHASE_READER(name)
 #endif
 
-// T = (I - U)^-1 for a strictly upper triangular 16x16 U (U[s][m], pitch PU, fp32), in fp32, by one
-// full warp.  Blocked: with U = [U11 U12; 0 U22] (8x8 blocks), T = [T11  T11 U12 T22; 0  T22] and
-// T11, T22 the inverses of the diagonal blocks.  Lanes 0-7 (mirrored in 16-23) back-substitute the
-// columns of T11, lanes 8-15 (mirrored in 24-31) those of T22: 7 dependent steps instead of 15.  The
-// lane pair (8+t, 24+t) then forms column t of U12 T22 (four rows each, exchanged by shuffle) and of
-// T11 (U12 T22).  Result rounded to TF32 and stored transposed (Tt[t][s]) or, with NATURAL, as T[s][t].
+// T = (I - U)^-1 for a strictly upper triangular 16x16 U (U[s][m], pitch PU, 16-byte aligned rows,
+// fp32), by back substitution in fp32; lane t (< 16) owns column t:
+//   T[s,t] = [s == t] + sum_{m>s} U[s,m] T[m,t]      (rows s = 14 .. 0; zero below the diagonal by itself)
+// Software-pipelined: the sum of row s is split into its newest term (m = s+1), the second newest
+// (m = s+2) and the rest (m >= s+3); the rest of row s-1 is accumulated between the two final FMAs
+// of row s, so one FMA per row sits on the dependent chain, and rows are fetched (float4) three rows
+// ahead.  Measured alone on a B200: 530 cycles against 620 for the plain loop and 890 for a 2x2
+// blocked variant with a shared-memory exchange.  Result rounded to TF32 and stored transposed
+// (Tt[t][s]) or, with NATURAL, as T[s][t].  Called by one full warp.
 template <bool NATURAL = false>
 __device__ __forceinline__ void tri_inverse(const float* U, float* Tt, int lane) {
-    const int blk = (lane >> 3) & 1, t = lane & 7, hi = lane >> 4, o = 8 * blk;
-    auto idx = [](int s, int c) { return NATURAL ? s * PU + c : c * PU + s; };
-    float col[8];
+    const int t = lane & 15;
+    float col[L], tp[L];
+    float4 rw[L][4];
 #pragma unroll
-    for (int m = 0; m < 8; ++m) col[m] = (m == t) ? 1.f : 0.f;
+    for (int s = 0; s < L; ++s) tp[s] = (s == t) ? 1.f : 0.f;
+    col[L - 1] = tp[L - 1];
+    auto load_row = [&](int s) {
 #pragma unroll
-    for (int s = 6; s >= 0; --s) {
-        // T[s,t] = sum_{m>s} U[s,m] T[m,t]   (zero for s >= t because col[m>t] = 0)
-        const float4 u0 = *reinterpret_cast<const float4*>(U + (o + s) * PU + o);
-        const float4 u1 = *reinterpret_cast<const float4*>(U + (o + s) * PU + o + 4);
-        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-        float acc0 = 0.f, acc1 = 0.f;
+        for (int q = 0; q < 4; ++q)
+            if (4 * q + 3 >= s + 1) rw[s][q] = *reinterpret_cast<const float4*>(U + s * PU + 4 * q);
+    };
+    auto u = [&](int s, int m) {
+        const float4 rr = rw[s][m >> 2];
+        return (m & 3) == 0 ? rr.x : (m & 3) == 1 ? rr.y : (m & 3) == 2 ? rr.z : rr.w;
+    };
+    load_row(14); load_row(13); load_row(12);
 #pragma unroll
-        for (int m = s + 1; m < 8; ++m) {
-            if ((m - s) & 1) acc0 = fmaf(u[m], col[m], acc0);
-            else acc1 = fmaf(u[m], col[m], acc1);
-        }
-        if (s < t) col[s] = acc0 + acc1;
-    }
-    // T11 goes out unrounded for now (it is an operand below), T22 and the zero block are final
-    if (hi == 0) {
+    for (int s = L - 2; s >= 0; --s) {
+        if (s >= 3) load_row(s - 3);
+        float x = tp[s];
+        if (s + 2 < L) x = fmaf(u(s, s + 2), col[s + 2], x);
+        if (s >= 1) {   // rest of row s-1: m >= s+2, all of those columns are final
+            float a0 = tp[s - 1], a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) Tt[idx(o + s, o + t)] = blk ? tf32f(col[s]) : col[s];
-    } else if (blk == 0) {
-#pragma unroll
-        for (int s = 0; s < 8; ++s) Tt[idx(8 + s, t)] = 0.f;
-    }
-    __syncwarp();
-    // column t of M = U12 T22: rows 4*hi .. 4*hi+3 in this lane, the other four from the mirror lane
-    float mv[4], mo[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float* ur = U + (4 * hi + q) * PU + 8;
-        const float4 u0 = *reinterpret_cast<const float4*>(ur), u1 = *reinterpret_cast<const float4*>(ur + 4);
-        mv[q] = fmaf(u0.x, col[0], fmaf(u0.y, col[1], fmaf(u0.z, col[2], u0.w * col[3]))) +
-                fmaf(u1.x, col[4], fmaf(u1.y, col[5], fmaf(u1.z, col[6], u1.w * col[7])));
-    }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) mo[q] = __shfl_xor_sync(0xffffffffu, mv[q], 16);
-    if (blk == 1) {
-        float M[8];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            M[q] = hi ? mo[q] : mv[q];
-            M[4 + q] = hi ? mv[q] : mo[q];
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {          // T12[s][t] = sum_m T11[s][m] M[m]  (T11 has its unit diagonal and zeros below it)
-            const int s = 4 * hi + q;
-            float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-            for (int m = 0; m < 8; m += 2) {
-                acc0 = fmaf(Tt[idx(s, m)], M[m], acc0);
-                acc1 = fmaf(Tt[idx(s, m + 1)], M[m + 1], acc1);
+            for (int m = s + 2; m < L; ++m) {
+                const float uu = u(s - 1, m);
+                if ((m & 3) == 0) a0 = fmaf(uu, col[m], a0);
+                else if ((m & 3) == 1) a1 = fmaf(uu, col[m], a1);
+                else if ((m & 3) == 2) a2 = fmaf(uu, col[m], a2);
+                else a3 = fmaf(uu, col[m], a3);
             }
-            Tt[idx(s, 8 + t)] = tf32f(acc0 + acc1);
+            tp[s - 1] = (a0 + a1) + (a2 + a3);
         }
+        col[s] = fmaf(u(s, s + 1), col[s + 1], x);
     }
-    __syncwarp();
-    if (hi == 0 && blk == 0) {
+    if (lane < 16) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s) Tt[idx(s, t)] = tf32f(col[s]);
+        for (int s = 0; s < L; ++s) Tt[NATURAL ? s * PU + t : t * PU + s] = tf32f(col[s]);
     }
 }
 
