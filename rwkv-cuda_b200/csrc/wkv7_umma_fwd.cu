@@ -20,6 +20,10 @@
 // Shared-memory operands use the canonical K-major, unswizzled layout: 16-byte (4 x tf32) pieces
 // of K; piece kc of row r at kc*LBO + r*16 bytes (8-row groups 128 bytes apart = SBO); LBO carries
 // 16 bytes of padding so that the elementwise writers hit distinct banks.
+// Inputs do not pass through shared memory: thread (channel pair p = lane, token group = warp) loads
+// its 2 channels x 4 tokens of r, w, k, v, a, b as 32-bit bf16 pairs straight into registers, one
+// chunk ahead (a warp reads the 128 contiguous bytes of one token), and writes the scaled operands
+// from there.
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code and leaves.
 #include "wkv7_umma.cuh"
 #include "wkv7_dispatch.cuh"
@@ -33,15 +37,14 @@ constexpr int kColS = 0, kColX = 64, kColU = 96;
 __device__ int g_umma_error = 0;      // 0 = fine; otherwise which wait expired (1 or 2) in some CTA
 
 struct Smem {
-    static constexpr int kRawBytes = 6 * L * N * 2;              // bf16 [6][L*N]: one stage, refilled as soon as prep has read it
-    static constexpr int kARt = kRawBytes;                        // [A~;R~]   16 pieces x LBO_T
+    static constexpr int kARt = 0;                                // [A~;R~]   16 pieces x LBO_T
     static constexpr int kBKt = kARt + 16 * LBO_T;                // [B~;K~]
     static constexpr int kBKc = kBKt + 16 * LBO_T + 1024;         // [b~|k~] by channel, 8 pieces x LBO_C (+ slack: BKt is read as 64 rows)
     static constexpr int kSAV = kBKc + 8 * LBO_C;                 // [SA|V] by channel
     static constexpr int kU = kSAV + 8 * LBO_C;                   // Uab Uak Ubr Ukr Tt, 5 x L*PU floats
     static constexpr int kWe = kU + 5 * L * PU * 4;               // [N] floats
-    static constexpr int kHalf = kWe + N * 4;                     // [2][N]
-    static constexpr int kBar = kHalf + 2 * N * 4;                // 2 mbarriers + tmem slot
+    static constexpr int kHalf = kWe + N * 4;                     // [4][N] log-decay sums of the four token groups
+    static constexpr int kBar = kHalf + 4 * N * 4;                // 2 mbarriers + tmem slot
     static constexpr int kBytes = kBar + 32;
 };
 static_assert(2 * L * PS * 4 <= 2 * 16 * LBO_T, "y/sa staging reuses the token-major operand arrays");
@@ -52,7 +55,6 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
                      const bf16* __restrict__ a_, const bf16* __restrict__ b_, bf16* __restrict__ y_,
                      float* __restrict__ sT_, float* __restrict__ ck_, float* __restrict__ sa_) {
     extern __shared__ __align__(128) unsigned char smem[];
-    bf16* raw = reinterpret_cast<bf16*>(smem);
     unsigned char *ARt = smem + Smem::kARt, *BKt = smem + Smem::kBKt, *BKc = smem + Smem::kBKc, *SAV = smem + Smem::kSAV;
     float* Um = reinterpret_cast<float*>(smem + Smem::kU);
     float *Uab = Um, *Uak = Um + L * PU, *Ubr = Um + 2 * L * PU, *Ukr = Um + 3 * L * PU, *Tt = Um + 4 * L * PU;
@@ -108,81 +110,73 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     }
 
     const int lrow = tid >> 3, lseg = tid & 7;
-    auto issue_loads = [&](int c) {
-        const i64 off = tok0 + (i64)(c * L + lrow) * C + lseg * 8;
+    // raw inputs of the next chunk: nx[x][q] = channels (2*lane, 2*lane+1) of tensor x at token 4*warp + q
+    uint32_t nx[6][4];
+    auto fetch = [&](int c) {
+        const i64 off = tok0 + (i64)(c * L + 4 * warp) * C + 2 * lane;
 #pragma unroll
-        for (int x = 0; x < 6; ++x) cp_async16(raw + (x * L + lrow) * N + lseg * 8, src[x] + off);
-        cp_async_commit();
+        for (int x = 0; x < 6; ++x)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) nx[x][q] = __ldg(reinterpret_cast<const unsigned int*>(src[x] + off + (i64)q * C));
     };
-    issue_loads(0);
+    fetch(0);
     int fail = 0;
 
     WKV7_PHASE_BEGIN();
     for (int c = 0; c < nchunks; ++c) {
         const uint32_t par = c & 1;
-        cp_async_wait<0>();
         tc_fence_before();
         if (__syncthreads_or(fail)) break;
         tc_fence_after();
-        const bf16* R = raw + 0 * L * N;
-        const bf16* Wr = raw + 1 * L * N;
-        const bf16* K = raw + 2 * L * N;
-        const bf16* V = raw + 3 * L * N;
-        const bf16* A = raw + 4 * L * N;
-        const bf16* Bv = raw + 5 * L * N;
-
-        WKV7_PHASE(0);   // wait for input tiles
-        // ---- prep: thread = (channel j, half of the chunk) ------------------------------------
+        WKV7_PHASE(0);   // top barrier
+        // ---- prep: thread = (channel pair 2*lane, 2*lane+1; tokens 4*warp .. 4*warp+3) --------------
         {
-            const int j = tid & 63, hf = tid >> 6, t0 = hf * 8;
-            float cs[8];
-            float run = 0.f;
+            const int j0 = 2 * lane, t0 = 4 * warp;
+            float cs[4][2];
+            float run0 = 0.f, run1 = 0.f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float x = to_f(Wr[(t0 + q) * N + j]);
-                run = fmaf(kWScale2, frcp(1.f + fexp(-x)), run);
-                cs[q] = run;
+            for (int q = 0; q < 4; ++q) {
+                const float2 x = bf16x2_to_f2(nx[1][q]);
+                run0 = fmaf(kWScale2, frcp(1.f + fexp(-x.x)), run0);
+                run1 = fmaf(kWScale2, frcp(1.f + fexp(-x.y)), run1);
+                cs[q][0] = run0; cs[q][1] = run1;
             }
-            WKV7_PHASE(8);   // prep: log-decays of the half chunk
-            Hs[hf * N + j] = run;
+            WKV7_PHASE(8);   // prep: log-decays of the token group
+            *reinterpret_cast<float2*>(Hs + warp * N + j0) = make_float2(run0, run1);
             __syncthreads();
             WKV7_PHASE(9);   // prep: exchange barrier
-            const float base = hf ? Hs[j] : 0.f;
-            if (hf == 0) We[j] = fex2(Hs[j] + Hs[N + j]);
-            float wprev = hf ? fex2(base) : 1.f;
-            float bt[8], kt[8], vv[8];
-            // loads of a batch of four tokens before its stores (tiles and operand arrays share one
-            // shared-memory block: the compiler keeps a load behind every earlier store)
+            float base0 = 0.f, base1 = 0.f, tot0 = 0.f, tot1 = 0.f;
 #pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                float xa[4], xr[4], wt[4];
+            for (int gq = 0; gq < 4; ++gq) {
+                const float2 h = *reinterpret_cast<const float2*>(Hs + gq * N + j0);
+                if (gq < warp) { base0 += h.x; base1 += h.y; }
+                tot0 += h.x; tot1 += h.y;
+            }
+            if (warp == 0) *reinterpret_cast<float2*>(We + j0) = make_float2(fex2(tot0), fex2(tot1));
+            float wp0 = fex2(base0), wp1 = fex2(base1);
+            float bt[4][2], kt[4][2], vv[4][2];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int tt = t0 + 4 * hb + q, qq = 4 * hb + q;
-                    xa[q] = to_f(A[tt * N + j]); xr[q] = to_f(R[tt * N + j]);
-                    const float lam = base + cs[qq];
-                    wt[q] = fex2(lam);
-                    const float iw = fex2(-lam);
-                    bt[qq] = tf32f(to_f(Bv[tt * N + j]) * iw);
-                    kt[qq] = tf32f(to_f(K[tt * N + j]) * iw);
-                    vv[qq] = to_f(V[tt * N + j]);
-                }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int tt = t0 + 4 * hb + q, qq = 4 * hb + q;
-                    *reinterpret_cast<float*>(ARt + canon(tt, j, LBO_T)) = tf32f(xa[q] * wprev);
-                    *reinterpret_cast<float*>(ARt + canon(16 + tt, j, LBO_T)) = tf32f(xr[q] * wt[q]);
-                    *reinterpret_cast<float*>(BKt + canon(tt, j, LBO_T)) = bt[qq];
-                    *reinterpret_cast<float*>(BKt + canon(16 + tt, j, LBO_T)) = kt[qq];
-                    wprev = wt[q];
-                }
+            for (int q = 0; q < 4; ++q) {
+                const int tt = t0 + q;
+                const float lam0 = base0 + cs[q][0], lam1 = base1 + cs[q][1];
+                const float wt0 = fex2(lam0), wt1 = fex2(lam1), iw0 = fex2(-lam0), iw1 = fex2(-lam1);
+                const float2 r2 = bf16x2_to_f2(nx[0][q]), k2 = bf16x2_to_f2(nx[2][q]), v2 = bf16x2_to_f2(nx[3][q]);
+                const float2 a2 = bf16x2_to_f2(nx[4][q]), b2 = bf16x2_to_f2(nx[5][q]);
+                bt[q][0] = tf32f(b2.x * iw0); bt[q][1] = tf32f(b2.y * iw1);
+                kt[q][0] = tf32f(k2.x * iw0); kt[q][1] = tf32f(k2.y * iw1);
+                vv[q][0] = v2.x; vv[q][1] = v2.y;
+                *reinterpret_cast<float2*>(ARt + canon(tt, j0, LBO_T)) = make_float2(tf32f(a2.x * wp0), tf32f(a2.y * wp1));
+                *reinterpret_cast<float2*>(ARt + canon(16 + tt, j0, LBO_T)) = make_float2(tf32f(r2.x * wt0), tf32f(r2.y * wt1));
+                *reinterpret_cast<float2*>(BKt + canon(tt, j0, LBO_T)) = make_float2(bt[q][0], bt[q][1]);
+                *reinterpret_cast<float2*>(BKt + canon(16 + tt, j0, LBO_T)) = make_float2(kt[q][0], kt[q][1]);
+                wp0 = wt0; wp1 = wt1;
             }
             // by channel: row j, K index = token (b~: 0..15, k~: 16..31; v: 16..31 of SAV)
 #pragma unroll
-            for (int q4 = 0; q4 < 2; ++q4) {
-                *reinterpret_cast<float4*>(BKc + canon(j, t0 + 4 * q4, LBO_C)) = make_float4(bt[4 * q4], bt[4 * q4 + 1], bt[4 * q4 + 2], bt[4 * q4 + 3]);
-                *reinterpret_cast<float4*>(BKc + canon(j, 16 + t0 + 4 * q4, LBO_C)) = make_float4(kt[4 * q4], kt[4 * q4 + 1], kt[4 * q4 + 2], kt[4 * q4 + 3]);
-                *reinterpret_cast<float4*>(SAV + canon(j, 16 + t0 + 4 * q4, LBO_C)) = make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]);
+            for (int ch = 0; ch < 2; ++ch) {
+                *reinterpret_cast<float4*>(BKc + canon(j0 + ch, t0, LBO_C)) = make_float4(bt[0][ch], bt[1][ch], bt[2][ch], bt[3][ch]);
+                *reinterpret_cast<float4*>(BKc + canon(j0 + ch, 16 + t0, LBO_C)) = make_float4(kt[0][ch], kt[1][ch], kt[2][ch], kt[3][ch]);
+                *reinterpret_cast<float4*>(SAV + canon(j0 + ch, 16 + t0, LBO_C)) = make_float4(vv[0][ch], vv[1][ch], vv[2][ch], vv[3][ch]);
             }
         }
         WKV7_PHASE(10);  // prep: scaled operands
@@ -190,7 +184,7 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
-        if (c + 1 < nchunks) issue_loads(c + 1);   // the input tiles have been consumed: refill them now
+        if (c + 1 < nchunks) fetch(c + 1);   // the registers are free again: request the next chunk
 
         WKV7_PHASE(1);   // prep + barrier
         // ---- U = [B~;K~][A~|R~]^T and X = S [A~|R~]^T on the tensor core ------------------------
