@@ -102,7 +102,7 @@ class V7Workload:
     # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel per token, from the ncu
     # capture of the reduced case (profiles/wkv7_default_path_tcgen05_fwd_mma_bwd_B8_T1024.md); traffic is
     # proportional to the token count
-    dram_bytes_per_token_bwd = (1.149506e9 + 0.387098e9) / (8 * 1024)
+    dram_bytes_per_token_bwd = (1.149294e9 + 0.388178e9) / (8 * 1024)
 
     def e2e_step(self):
         """Host buffers in, host buffers out, through the public host-buffer API
