@@ -33,6 +33,11 @@ constexpr float kWScale2 = kWScale * 1.4426950408889634f;   // the same in log2 
 // CTAs of an SM hit at the same time during operand preparation.
 __device__ __forceinline__ uint32_t tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 __device__ __forceinline__ float tf32f(float x) { return __uint_as_float(tf32(x)); }
+// The same rounding for a value that only ever feeds a tensor-core operand: the tensor core reads the
+// upper 19 bits of a TF32 operand register or shared-memory word and ignores the rest, so adding
+// half a unit of the last kept place is enough (one instruction; results are bit-identical to tf32()).
+__device__ __forceinline__ uint32_t tf32r(float x) { return __float_as_uint(x) + 0x1000u; }
+__device__ __forceinline__ float tf32rf(float x) { return __uint_as_float(tf32r(x)); }
 
 // Single-instruction approximations (flush-to-zero forms: no denormal fix-up code around them).
 // Their arguments here are decays >= 6e-5, sums 1 + e^x and log-decays in [-10, 0].
@@ -213,8 +218,8 @@ template <int KS>
 __device__ __forceinline__ void acc_to_a(uint32_t (*areg)[4], const float (*acc)[4]) {
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
-        areg[ks][0] = tf32(acc[ks][0]); areg[ks][1] = tf32(acc[ks][2]);
-        areg[ks][2] = tf32(acc[ks][1]); areg[ks][3] = tf32(acc[ks][3]);
+        areg[ks][0] = tf32r(acc[ks][0]); areg[ks][1] = tf32r(acc[ks][2]);
+        areg[ks][2] = tf32r(acc[ks][1]); areg[ks][3] = tf32r(acc[ks][3]);
     }
 }
 
@@ -299,7 +304,7 @@ __device__ __forceinline__ void tri_inverse(const float* U, float* Tt, int lane)
     }
     if (lane < 16) {
 #pragma unroll
-        for (int s = 0; s < L; ++s) Tt[NATURAL ? s * PU + t : t * PU + s] = tf32f(col[s]);
+        for (int s = 0; s < L; ++s) Tt[NATURAL ? s * PU + t : t * PU + s] = tf32rf(col[s]);
     }
 }
 

@@ -168,10 +168,10 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int tt = t0 + 4 * hb + q;
-                    At[tt * PK + jp] = tf32f(xa[q] * wprev);
-                    Rt[tt * PK + jp] = tf32f(xr[q] * wt[q]);
-                    Bt[tt * PK + jp] = tf32f(xb[q] * iw[q]);
-                    Kt[tt * PK + jp] = tf32f(xk[q] * iw[q]);
+                    At[tt * PK + jp] = tf32rf(xa[q] * wprev);
+                    Rt[tt * PK + jp] = tf32rf(xr[q] * wt[q]);
+                    Bt[tt * PK + jp] = tf32rf(xb[q] * iw[q]);
+                    Kt[tt * PK + jp] = tf32rf(xk[q] * iw[q]);
                     Vf[tt * PK + ip] = xv[q];
                     dYf[tt * PK + ip] = xd[q];
                     Wt[tt * PK + j] = wt[q];
@@ -200,7 +200,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     const int s = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
                     const bool keep = strict ? (s < tt) : (s <= tt);
                     const float val = keep ? U[nt][e] : 0.f;
-                    dst[s * PU + tt] = warp == 0 ? val : tf32f(val);
+                    dst[s * PU + tt] = warp == 0 ? val : tf32rf(val);
                 }
             if (warp == 0) {
                 __syncwarp();
@@ -223,7 +223,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         float X2[4][4] = {};
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t a0 = tf32(E[ks][0]), a1 = tf32(E[ks][2]), a2 = tf32(E[ks][1]), a3 = tf32(E[ks][3]);
+            const uint32_t a0 = tf32r(E[ks][0]), a1 = tf32r(E[ks][2]), a2 = tf32r(E[ks][1]), a3 = tf32r(E[ks][3]);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const float* pb = Bt + (nt * 8 + g) * PK + ks * 8 + t;
@@ -241,8 +241,8 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         {   // sa arrived as fp32: round it to TF32 once (it is only ever an MMA operand here)
             float4* p = reinterpret_cast<float4*>(SAs + lrow * PT + lseg * 8);
             float4 x0 = p[0], x1 = p[1];
-            x0.x = tf32f(x0.x); x0.y = tf32f(x0.y); x0.z = tf32f(x0.z); x0.w = tf32f(x0.w);
-            x1.x = tf32f(x1.x); x1.y = tf32f(x1.y); x1.z = tf32f(x1.z); x1.w = tf32f(x1.w);
+            x0.x = tf32rf(x0.x); x0.y = tf32rf(x0.y); x0.z = tf32rf(x0.z); x0.w = tf32rf(x0.w);
+            x1.x = tf32rf(x1.x); x1.y = tf32rf(x1.y); x1.z = tf32rf(x1.z); x1.w = tf32rf(x1.w);
             p[0] = x0; p[1] = x1;
         }
         uint32_t dyreg[2][4], xreg[2][4], evreg[2][4];
@@ -260,7 +260,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             for (int e = 0; e < 4; ++e) {
                 const int i = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
                 store_bf16(dv_ + tok0 + (i64)(c * L + tt) * C + i, X2[2 + nt][e]);
-                EVs[tt * PK + (i & ~7) + perm8(i & 7)] = tf32f(EV[nt][e]);
+                EVs[tt * PK + (i & ~7) + perm8(i & 7)] = tf32rf(EV[nt][e]);
             }
         WKV7_PHASE(5);   // EV chain, dV
         __syncthreads();
@@ -280,10 +280,10 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         float Z1[4][4] = {}, Z2[4][4] = {};
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t a0 = tf32(ET[ks][0]), a1 = tf32(ET[ks][2]), a2 = tf32(ET[ks][1]), a3 = tf32(ET[ks][3]);
+            const uint32_t a0 = tf32r(ET[ks][0]), a1 = tf32r(ET[ks][2]), a2 = tf32r(ET[ks][1]), a3 = tf32r(ET[ks][3]);
             const float* p0 = S0 + (ks * 8 + 2 * t) * PS0 + row0 + 2 * g;   // A[m=j][k=i] = S0[i][j], rows (g, g+8) = real (2g, 2g+1)
             const float2 sx = *reinterpret_cast<const float2*>(p0), sy = *reinterpret_cast<const float2*>(p0 + PS0);
-            const uint32_t s0a = tf32(sx.x), s1a = tf32(sx.y), s2a = tf32(sy.x), s3a = tf32(sy.y);
+            const uint32_t s0a = tf32r(sx.x), s1a = tf32r(sx.y), s2a = tf32r(sy.x), s3a = tf32r(sy.y);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const float* pv = Vf + (nt * 8 + g) * PK + ks * 8 + t;
@@ -308,7 +308,7 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int e = 0; e < 4; ++e) {
                     const int u = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
                     const bool keep = strict ? (u > tt) : (u >= tt);
-                    const float val = tf32f(keep ? P[nt][e] : 0.f);
+                    const float val = tf32rf(keep ? P[nt][e] : 0.f);
                     pn[u * PU + tt] = val;
                     pt[tt * PU + u] = val;
                 }
@@ -338,10 +338,10 @@ wkv7c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int e = 2 * uh + h;
-                    atreg[ks][e] = tf32(xa[h]); atlo[ks][e] = tf32(xa[h] - __uint_as_float(atreg[ks][e]));
-                    rtreg[ks][e] = tf32(xr[h]); rtlo[ks][e] = tf32(xr[h] - __uint_as_float(rtreg[ks][e]));
-                    btreg[ks][e] = tf32(xb[h]); btlo[ks][e] = tf32(xb[h] - __uint_as_float(btreg[ks][e]));
-                    ktreg[ks][e] = tf32(xk[h]); ktlo[ks][e] = tf32(xk[h] - __uint_as_float(ktreg[ks][e]));
+                    atreg[ks][e] = tf32(xa[h]); atlo[ks][e] = tf32r(xa[h] - __uint_as_float(atreg[ks][e]));
+                    rtreg[ks][e] = tf32(xr[h]); rtlo[ks][e] = tf32r(xr[h] - __uint_as_float(rtreg[ks][e]));
+                    btreg[ks][e] = tf32(xb[h]); btlo[ks][e] = tf32r(xb[h] - __uint_as_float(btreg[ks][e]));
+                    ktreg[ks][e] = tf32(xk[h]); ktlo[ks][e] = tf32r(xk[h] - __uint_as_float(ktreg[ks][e]));
                 }
                 wp2 = wu2;
             }

@@ -162,11 +162,11 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
                 const float wt0 = fex2(lam0), wt1 = fex2(lam1), iw0 = fex2(-lam0), iw1 = fex2(-lam1);
                 const float2 r2 = bf16x2_to_f2(nx[0][q]), k2 = bf16x2_to_f2(nx[2][q]), v2 = bf16x2_to_f2(nx[3][q]);
                 const float2 a2 = bf16x2_to_f2(nx[4][q]), b2 = bf16x2_to_f2(nx[5][q]);
-                bt[q][0] = tf32f(b2.x * iw0); bt[q][1] = tf32f(b2.y * iw1);
-                kt[q][0] = tf32f(k2.x * iw0); kt[q][1] = tf32f(k2.y * iw1);
+                bt[q][0] = tf32rf(b2.x * iw0); bt[q][1] = tf32rf(b2.y * iw1);
+                kt[q][0] = tf32rf(k2.x * iw0); kt[q][1] = tf32rf(k2.y * iw1);
                 vv[q][0] = v2.x; vv[q][1] = v2.y;
-                *reinterpret_cast<float2*>(ARt + canon(tt, j0, LBO_T)) = make_float2(tf32f(a2.x * wp0), tf32f(a2.y * wp1));
-                *reinterpret_cast<float2*>(ARt + canon(16 + tt, j0, LBO_T)) = make_float2(tf32f(r2.x * wt0), tf32f(r2.y * wt1));
+                *reinterpret_cast<float2*>(ARt + canon(tt, j0, LBO_T)) = make_float2(tf32rf(a2.x * wp0), tf32rf(a2.y * wp1));
+                *reinterpret_cast<float2*>(ARt + canon(16 + tt, j0, LBO_T)) = make_float2(tf32rf(r2.x * wt0), tf32rf(r2.y * wt1));
                 *reinterpret_cast<float2*>(BKt + canon(tt, j0, LBO_T)) = make_float2(bt[q][0], bt[q][1]);
                 *reinterpret_cast<float2*>(BKt + canon(16 + tt, j0, LBO_T)) = make_float2(kt[q][0], kt[q][1]);
                 wp0 = wt0; wp1 = wt1;
@@ -218,8 +218,8 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
                 for (int e = 0; e < 4; ++e) {
                     const int s = g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
                     const float ua = s < tt ? U[nt][e] : 0.f, ur = s <= tt ? U[2 + nt][e] : 0.f;
-                    if (warp == 0) dstA[s * PU + tt] = ua; else dstA[tt * PU + s] = tf32f(ua);
-                    dstR[tt * PU + s] = tf32f(ur);
+                    if (warp == 0) dstA[s * PU + tt] = ua; else dstA[tt * PU + s] = tf32rf(ua);
+                    dstR[tt * PU + s] = tf32rf(ur);
                 }
             if (warp == 0) {
                 __syncwarp();
@@ -254,8 +254,8 @@ wkv7u_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const int s = nt * 8 + 2 * t;
-            *reinterpret_cast<float2*>(SAV + canon(row0 + g, s, LBO_C)) = make_float2(tf32f(SA[nt][0]), tf32f(SA[nt][1]));
-            *reinterpret_cast<float2*>(SAV + canon(row0 + g + 8, s, LBO_C)) = make_float2(tf32f(SA[nt][2]), tf32f(SA[nt][3]));
+            *reinterpret_cast<float2*>(SAV + canon(row0 + g, s, LBO_C)) = make_float2(tf32rf(SA[nt][0]), tf32rf(SA[nt][1]));
+            *reinterpret_cast<float2*>(SAV + canon(row0 + g + 8, s, LBO_C)) = make_float2(tf32rf(SA[nt][2]), tf32rf(SA[nt][3]));
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
