@@ -391,7 +391,7 @@ def main():
     ap.add_argument("--cpu-seq", type=int, default=256, help="sequence length of one CPU-baseline step (B=1, C=4096)")
     ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
     ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
-    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2, 3, 4],
+    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="RWKV-7 kernel family (rwkvb200_wkv7_select_path); 0 = automatic")
     ap.add_argument("--op", default="wkv7", choices=["wkv7", "wkv4", "timex", "wkv5", "wkv6state"],
                     help="wkv7 = the headline configuration (default); the others are BASELINE configurations 1-4")

@@ -45,11 +45,20 @@ extern "C" int rwkvb200_version(void) { return 100; }
 extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 
 // 0 = automatic (= 3 where applicable), 1 = general-shape kernels only, 2 = mma.sync chunked kernels,
-// 3 = tcgen05 forward + chunked backward, 4 = tcgen05 forward and backward
+// 3 = tcgen05 forward + chunked backward, 4 = tcgen05 forward and backward,
+// 5 = tcgen05 forward + producer/consumer chunked backward.  Automatic takes 5 instead of 3 when the
+// launch puts at most one (batch, head) unit on an SM.
 static int g_wkv7_path = 0;
 
+static int sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return 0;
+    return n;
+}
+
 extern "C" int rwkvb200_wkv7_select_path(int path) {
-    RWKV_REQUIRE(path >= 0 && path <= 4, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..4", path);
+    RWKV_REQUIRE(path >= 0 && path <= 5, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..5", path);
     g_wkv7_path = path;
     return RWKVB200_OK;
 }
@@ -122,6 +131,11 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
         if (g_wkv7_path == 4)
             return wkv7_umma_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
                                       as_stream(stream));
+        // one unit per SM or fewer: the time is one unit's chain of chunks, which the producer/consumer
+        // kernel shortens; with more units per SM two plain CTAs per SM give more throughput
+        if (g_wkv7_path == 5 || (g_wkv7_path == 0 && (long long)B * H <= sm_count()))
+            return wkv7_split_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
+                                       as_stream(stream));
         return wkv7_chunked_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
                                      as_stream(stream));
     }

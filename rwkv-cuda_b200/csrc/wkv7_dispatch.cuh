@@ -27,6 +27,12 @@ int wkv7_umma_backward(int B, int T, int H, const void* r, const void* w, const 
                        cudaStream_t st);
 int wkv7_umma_bwd_error();
 
+// the same backward as a producer/consumer pair of warp groups (one CTA per SM; for small grids)
+int wkv7_split_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v,
+                        const void* a, const void* b, const void* dy, const float* dsT, const float* s,
+                        const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,
+                        cudaStream_t st);
+
 int wkv7_chunked_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v,
                           const void* a, const void* b, const void* dy, const float* dsT, const float* s,
                           const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,

@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[2, 3, 4], ids=["mma_sync", "tcgen05_fwd", "tcgen05_fwd_bwd"])
+@pytest.fixture(params=[2, 3, 4, 5], ids=["mma_sync", "tcgen05_fwd", "tcgen05_fwd_bwd", "split_bwd"])
 def R(request):
     """2 = mma.sync chunked kernels, 3 = tcgen05 forward with the same backward."""
     import rwkv_cuda_b200 as R
@@ -76,3 +76,27 @@ def test_forward_backward(R, B, T, H, use_s0, use_sT):
     names = ["y", "dr", "dw", "dk", "dv", "da", "db"] + (["ds0"] if use_s0 else []) + (["sT"] if use_sT else [])
     rep = {n: "%.2e" % Hh.assert_close(out[n], want[n], Hh.TOL_BF16, n)[1] for n in names}
     print(rep)
+
+
+def _set_path(p):
+    from rwkv_cuda_b200 import _lib
+    _lib.call("rwkvb200_wkv7_select_path", p)
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 64, 3), (3, 32, 64)])
+def test_backward_kernel_choice_is_bit_exact(B, T, H):
+    """The producer/consumer backward (small grids) and the plain one (B*H above the SM count) do the
+    same arithmetic in the same order: forced either way, and chosen automatically on both sides of
+    the threshold, they must agree bit for bit."""
+    import rwkv_cuda_b200 as R
+    inp = Hh.v7_inputs(B, T, H, 64, seed=11)
+    outs = {}
+    try:
+        for p in (3, 5, 0):
+            _set_path(p)
+            outs[p] = _run_both(R, inp, H, True, True)
+    finally:
+        _set_path(0)
+    for n in ("dr", "dw", "dk", "dv", "da", "db", "ds0"):
+        assert torch.equal(outs[3][n], outs[5][n]), n
+        assert torch.equal(outs[3][n], outs[0][n]), n
