@@ -191,8 +191,8 @@ int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len,
  * 0 = automatic (for bf16, N=64, chunk_len=16: setting 3, or 5 when B*H does not exceed the number
  *     of SMs; general-shape kernels otherwise),
  * 1 = general-shape kernels only, 2 = mma.sync tensor-core kernels, 3 = tcgen05 forward with the
- * mma.sync backward, 4 = tcgen05 forward and backward, 5 = tcgen05 forward with the
- * producer/consumer form of the mma.sync backward (2 to 5 refuse other shapes).
+ * mma.sync backward, 4 = tcgen05 forward and backward, 5 = the producer/consumer forms of the
+ * tcgen05 forward and the mma.sync backward (2 to 5 refuse other shapes).
  * The forward and the backward of one operator call must run under the same setting: the
  * layout of s / sa differs between the two kernel families.  No counterpart in the reference. */
 int rwkvb200_wkv7_select_path(int path);

@@ -21,6 +21,11 @@ int wkv7_umma_forward(int B, int T, int H, const float* s0, const void* r, const
                       const void* v, const void* a, const void* b, void* y, float* sT, float* s, float* sa,
                       cudaStream_t st);
 int wkv7_umma_error();
+// the same forward as a producer/consumer pair of warp groups (one CTA per SM; for small grids)
+int wkv7_umma_split_forward(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k,
+                            const void* v, const void* a, const void* b, void* y, float* sT, float* s, float* sa,
+                            cudaStream_t st);
+int wkv7_umma_split_error();
 int wkv7_umma_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v,
                        const void* a, const void* b, const void* dy, const float* dsT, const float* s,
                        const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,

@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[2, 3, 4, 5], ids=["mma_sync", "tcgen05_fwd", "tcgen05_fwd_bwd", "split_bwd"])
+@pytest.fixture(params=[2, 3, 4, 5], ids=["mma_sync", "tcgen05_fwd", "tcgen05_fwd_bwd", "producer_consumer"])
 def R(request):
     """2 = mma.sync chunked kernels, 3 = tcgen05 forward with the same backward."""
     import rwkv_cuda_b200 as R
@@ -84,8 +84,8 @@ def _set_path(p):
 
 
 @pytest.mark.parametrize("B,T,H", [(1, 64, 3), (3, 32, 64)])
-def test_backward_kernel_choice_is_bit_exact(B, T, H):
-    """The producer/consumer backward (small grids) and the plain one (B*H above the SM count) do the
+def test_kernel_choice_by_grid_size_is_bit_exact(B, T, H):
+    """The producer/consumer kernels (small grids) and the plain ones (B*H above the SM count) do the
     same arithmetic in the same order: forced either way, and chosen automatically on both sides of
     the threshold, they must agree bit for bit."""
     import rwkv_cuda_b200 as R
@@ -97,6 +97,6 @@ def test_backward_kernel_choice_is_bit_exact(B, T, H):
             outs[p] = _run_both(R, inp, H, True, True)
     finally:
         _set_path(0)
-    for n in ("dr", "dw", "dk", "dv", "da", "db", "ds0"):
+    for n in ("y", "sT", "dr", "dw", "dk", "dv", "da", "db", "ds0"):
         assert torch.equal(outs[3][n], outs[5][n]), n
         assert torch.equal(outs[3][n], outs[0][n]), n
