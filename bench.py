@@ -114,7 +114,7 @@ class V7Workload:
             self.host_out.update(sT=torch.empty_like(self.host_s0).pin_memory(), ds0=torch.empty_like(self.host_s0).pin_memory())
             self.host_named = dict(zip(("r", "w", "k", "v", "a", "b"), self.host_in))
             self.host_named.update(dy=self.host_dy, s0=self.host_s0, dsT=self.host_dsT)
-            self.pipe = names(self.T, self.H, self.N, self.dev, slice_batch=min(2, self.b))
+            self.pipe = names(self.T, self.H, self.N, self.dev, slice_batch=1)
         self.pipe.forward_backward(self.host_named, self.host_out)
 
     def e2e_bytes(self):

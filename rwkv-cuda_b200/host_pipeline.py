@@ -15,7 +15,7 @@ class Wkv7HostPipeline:
     IN = ("r", "w", "k", "v", "a", "b", "dy")
     OUT = ("y", "dr", "dw", "dk", "dv", "da", "db")
 
-    def __init__(self, T, H, N, device, slice_batch=2, depth=3, dtype=torch.bfloat16, chunk_len=16):
+    def __init__(self, T, H, N, device, slice_batch=1, depth=3, dtype=torch.bfloat16, chunk_len=16):
         self.T, self.H, self.N, self.sb, self.depth = T, H, N, slice_batch, depth
         self.dev = torch.device(device)
         self.h2d, self.comp, self.d2h = (torch.cuda.Stream(self.dev) for _ in range(3))
