@@ -109,9 +109,12 @@ int rwkvb200_wkv5a_backward(int dtype, int B, int T, int C, int H, const void* r
  * cuda_backward of wkv6/cuda/wkv6_cuda_v1.cu:211-223 (wkv6_op.cpp:8-13).
  *   w (B,T,C) fp32 = -exp(w_raw) (the kernel applies exp); gw (B,T,C) in `dtype` w.r.t.
  *   w_raw; gu (B,C) per-batch partials.
- *   `scratch`: device buffer of rwkvb200_wkv6_scratch_bytes(B,T,C) bytes used inside the
- *   backward (contents undefined afterwards).  No limit on T (the reference's backward
+ *   `scratch`: device buffer of rwkvb200_wkv6_scratch_bytes(B,T,C) bytes (16 per element) used
+ *   inside the backward (contents undefined afterwards).  No limit on T (the reference's backward
  *   fails for T >= 128, wkv6/run.py:51).
+ *   bf16 with head size 64 and T a multiple of 16 runs on chunked tensor-core kernels; if these
+ *   meet a chunk whose cumulative decay is too strong for that form (sum of |log w| over 16 tokens
+ *   above 80 in some channel) the general-shape kernels redo the call in the same stream.
  */
 size_t rwkvb200_wkv6_scratch_bytes(int B, int T, int C);
 int rwkvb200_wkv6_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,

@@ -21,6 +21,9 @@
 // so no per-thread history of states is kept (the reference keeps T*N floats per thread and
 // fails beyond T = 64..128) and T is unlimited.
 #include "common.cuh"
+#include "wkv6_chunked.cuh"
+#include <initializer_list>
+#include <type_traits>
 
 namespace rwkvb200 {
 namespace {
@@ -63,7 +66,9 @@ __global__ void __launch_bounds__(NMAX) wkv6_forward_kernel(int T, int C, int H,
                                                            const E* __restrict__ k_, const E* __restrict__ v_,
                                                            const void* __restrict__ w_, int w_raw,
                                                            const E* __restrict__ u_, const void* __restrict__ s0_,
-                                                           int s0_kind, E* __restrict__ y_, float* __restrict__ sT_) {
+                                                           int s0_kind, E* __restrict__ y_, float* __restrict__ sT_,
+                                                           const int* __restrict__ only_if_) {
+    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernel's result stands
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks, ds;
@@ -123,7 +128,8 @@ __global__ void __launch_bounds__(NMAX) wkv6_backward_kernel(
     const void* __restrict__ w_, int w_raw, const E* __restrict__ u_, const void* __restrict__ s0_, int s0_kind,
     const E* __restrict__ gy_, const float* __restrict__ dsT_, E* __restrict__ gr_, E* __restrict__ gk_,
     E* __restrict__ gv_, E* __restrict__ gw_, E* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind,
-    float* __restrict__ scratch_) {
+    float* __restrict__ scratch_, const int* __restrict__ only_if_) {
+    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernels' result stands
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks, vs, gs, ds;
@@ -235,13 +241,42 @@ __global__ void __launch_bounds__(NMAX) wkv6_backward_kernel(
     }
 }
 
+// Flags of the chunked kernels ("a chunk's decay was too strong"): a small ring, one slot per call, so
+// that calls in flight on different streams do not share one.
+static __device__ int g_wkv6_unsafe[64];
+static int* next_flag() {
+    static int* base = nullptr;
+    static unsigned counter = 0;
+    if (base == nullptr && cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_wkv6_unsafe) != cudaSuccess) return nullptr;
+    return base + (counter++ & 63);
+}
+static int g_wkv6_chunked_enabled = 1;
+
+template <typename E>
+bool chunked_ok(int T, int N, std::initializer_list<const void*> ps) {
+    if (!g_wkv6_chunked_enabled || !std::is_same<E, bf16>::value || N != 64 || T % 16 != 0) return false;
+    for (const void* p : ps)
+        if (p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) != 0) return false;
+    return true;
+}
+
 template <typename E>
 int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
                const void* u, const void* s0, int s0_kind, void* y, float* sT, cudaStream_t st, const char* what) {
     const int N = C / H;
+    const int* only_if = nullptr;
+    if (chunked_ok<E>(T, N, {r, k, v, w, u, s0, y, sT})) {
+        // tensor-core kernel first; the general-shape kernel below then only runs if that one found a
+        // chunk whose decay is too strong for the chunked form
+        int* flag = next_flag();
+        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "%s: no device flag", what);
+        cudaMemsetAsync(flag, 0, sizeof(int), st);
+        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, y, sT, nullptr, flag, st)) return e;
+        only_if = flag;
+    }
 #define RWKV_GO(NM)                                                                                              \
     wkv6_forward_kernel<E, NM><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, w, w_raw, \
-                                                      (const E*)u, s0, s0_kind, (E*)y, sT)
+                                                      (const E*)u, s0, s0_kind, (E*)y, sT, only_if)
     switch (head_capacity(N)) {
         case 32: RWKV_GO(32); break;
         case 64: RWKV_GO(64); break;
@@ -255,13 +290,27 @@ template <typename E>
 int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
                const void* u, const void* s0, int s0_kind, const void* gy, const float* dsT, void* gr, void* gk,
                void* gv, void* gw, void* gu, void* ds0, int ds0_kind, void* scratch, cudaStream_t st,
-               const char* what) {
+               const char* what, bool big_scratch = true) {
     const int N = C / H;
+    const int* only_if = nullptr;
+    if (big_scratch && chunked_ok<E>(T, N, {r, k, v, w, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0, scratch})) {
+        // tensor-core kernels first: a forward pass that leaves the chunk-start states in the scratch
+        // buffer, then the reverse pass; the general-shape kernel below then only runs if a chunk's decay
+        // was too strong for the chunked form (it reuses the front of the same scratch buffer)
+        int* flag = next_flag();
+        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "%s: no device flag", what);
+        cudaMemsetAsync(flag, 0, sizeof(int), st);
+        float* ck = static_cast<float*>(scratch);
+        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
+        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
+            return e;
+        only_if = flag;
+    }
 #define RWKV_GO(NM)                                                                                               \
     wkv6_backward_kernel<E, NM><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, w, w_raw, \
                                                        (const E*)u, s0, s0_kind, (const E*)gy, dsT, (E*)gr,       \
                                                        (E*)gk, (E*)gv, (E*)gw, (E*)gu, ds0, ds0_kind,             \
-                                                       (float*)scratch)
+                                                       (float*)scratch, only_if)
     switch (head_capacity(N)) {
         case 32: RWKV_GO(32); break;
         case 64: RWKV_GO(64); break;
@@ -287,7 +336,9 @@ using namespace rwkvb200;
 
 extern "C" size_t rwkvb200_wkv6_scratch_bytes(int B, int T, int C) {
     if (B <= 0 || T <= 0 || C <= 0) return 0;
-    return (size_t)B * T * C * sizeof(float);
+    // 16 bytes per element: the chunked backward (bf16, head size 64, T a multiple of 16) keeps one
+    // fp32 64x64 state per 16 tokens and head here; the general-shape backward uses the first quarter
+    return (size_t)B * T * C * sizeof(float) * 4;
 }
 
 extern "C" int rwkvb200_wkv6_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
@@ -360,9 +411,9 @@ extern "C" int rwkvb200_wkv6_backward_noalloc(int dtype, int B, int T, int C, in
     // nothing has to be cleared between calls.
     return dtype == RWKVB200_F32
                ? launch_bwd<float>(B, T, C, H, r, k, v, w, 0, u, nullptr, kNone, gy, nullptr, gr, gk, gv, gw, gu,
-                                   nullptr, kNone, scratch, as_stream(stream), "wkv6_backward_noalloc")
+                                   nullptr, kNone, scratch, as_stream(stream), "wkv6_backward_noalloc", false)
                : launch_bwd<bf16>(B, T, C, H, r, k, v, w, 0, u, nullptr, kNone, gy, nullptr, gr, gk, gv, gw, gu,
-                                  nullptr, kNone, scratch, as_stream(stream), "wkv6_backward_noalloc");
+                                  nullptr, kNone, scratch, as_stream(stream), "wkv6_backward_noalloc", false);
 }
 
 extern "C" int rwkvb200_wkv6state_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,

@@ -1,0 +1,21 @@
+// Launchers of the chunked (tensor-core) RWKV-6 kernels: bf16, head size 64, T a multiple of 16.
+#pragma once
+#include "common.cuh"
+
+namespace rwkvb200 {
+
+// s0_kind: 0 none, 1 bf16, 2 fp32 (one N x N block per (batch, head), [value][key]).  w: fp32
+// log-decay (w_raw = 0) or bf16 raw decay input (w_raw = 1, log-decay = -exp(w)).  ck: optional
+// fp32 (B,H,T/16,N,N) chunk-start states.  unsafe: device flag raised when a chunk's cumulative
+// decay is too strong for the chunked form (the results are then invalid).
+int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
+                         const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
+                         cudaStream_t st);
+
+// Backward; ck are the chunk-start states written by wkv6_chunked_forward on the same inputs
+// (fp32, (B,H,T/16,N,N)).  ds0_kind as s0_kind (0: no state gradient out).  gu is per batch: (B,C).
+int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
+                          const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st);
+
+}  // namespace rwkvb200

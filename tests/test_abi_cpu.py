@@ -62,7 +62,7 @@ def test_status_codes_without_launch():
     assert limit == 8 << 20
     assert L.rwkvb200_wkv6_backward_noalloc(1, 1, limit // 64 + 1, 64, 1, *([one] * 11), None) == -1
     assert b"exceeds the built-in scratch" in L.rwkvb200_last_error()
-    assert L.rwkvb200_wkv6_scratch_bytes(2, 3, 4) == 96
+    assert L.rwkvb200_wkv6_scratch_bytes(2, 3, 4) == 2 * 3 * 4 * 16
 
 
 def test_ops_refuse_cpu_tensors():

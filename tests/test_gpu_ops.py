@@ -215,7 +215,7 @@ def test_wkv6_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,H,N", [(2, 300, 2, 64), (2, 7, 2, 4), (1, 50, 1, 128), (2, 41, 3, 17)])
+@pytest.mark.parametrize("B,T,H,N", [(2, 300, 2, 64), (2, 256, 2, 64), (2, 7, 2, 4), (1, 50, 1, 128), (2, 41, 3, 17)])
 def test_wkv6_oracle(R, dtype, B, T, H, N):
     """T = 300 is beyond what the reference backward can run (wkv6/run.py:51)."""
     g = Hh.gen(42)
@@ -252,7 +252,7 @@ def test_wkv6state_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,H,N", [(2, 200, 2, 64), (3, 7, 2, 4)])
+@pytest.mark.parametrize("B,T,H,N", [(2, 200, 2, 64), (2, 192, 2, 64), (3, 7, 2, 4)])
 def test_wkv6state_oracle(R, dtype, B, T, H, N):
     g = Hh.gen(42)
     C = H * N
@@ -292,6 +292,29 @@ def test_wkv6state_ex_oracle(R, dtype):
     for got, want, name in zip((y, sT, gr, gk, gv, gw, gu.float().sum(0), ds0), wants,
                                ("y", "sT", "gr", "gk", "gv", "gw", "gu", "ds0")):
         Hh.assert_close(got, want, tol, f"wkv6state_ex {name}")
+
+
+@pytest.mark.parametrize("shift", [2.0, 5.0])
+def test_wkv6_strong_decay_falls_back(R, shift):
+    """bf16, N = 64, T a multiple of 16 takes the chunked tensor-core kernels, which divide by the
+    cumulative decay of a chunk.  With decays this strong (log-decay down to -e^6 per token) that
+    form is unusable: the kernel must notice and the general-shape kernels must redo the call."""
+    B, T, H, N = 2, 128, 2, 64
+    dtype = torch.bfloat16
+    g = Hh.gen(9)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.randn(g, B, T, C) + shift, Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv6(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv6(R, dtype, H, r, k, v, w_raw, u, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu")):
+        assert torch.isfinite(got.float()).all(), name
+        if name == "gw" and shift > 3:
+            continue   # e^5 and more per token: the decay gradient is below what bf16 inputs resolve
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv6 strong decay {name}")
 
 
 # ------------------------------------------------------------------ RWKV-7

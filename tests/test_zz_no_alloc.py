@@ -30,10 +30,14 @@ def _outputs(dtype, B, T, C):
     return big(), big(), big(), big(), torch.full((B, C), float("nan"), dtype=dtype, device=DEV)
 
 
+@pytest.mark.parametrize("T", [100, 96])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_noalloc_matches_regular_entry_point_twice(dtype):
+def test_noalloc_matches_regular_entry_point_twice(dtype, T):
     import rwkv_cuda_b200 as R
-    B, T, H, N = 2, 96, 3, 64
+    B, H, N = 2, 3, 64
+    # bf16 with T a multiple of 16 sends the regular entry point to the chunked tensor-core kernels;
+    # everything else runs the same general-shape kernel as the allocation-free entry point
+    same_kernel = not (dtype == torch.bfloat16 and T % 16 == 0)
     C = H * N
     for call_no, seed in enumerate((11, 12)):     # two calls in a row, different data
         rd, kd, vd, ew, ud, gd = _inputs(dtype, B, T, H, N, seed)
@@ -44,9 +48,9 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         torch.cuda.synchronize()
         for a, b, name in zip(got, want, ("gr", "gk", "gv", "gw", "gu")):
             assert torch.isfinite(a.float()).all(), f"call {call_no}: {name} has unwritten or non-finite elements"
-            # same kernel, same arithmetic: the tolerance of the parity tests is far wider than needed
             Hh.assert_close(a, b.double().cpu(), Hh.tol_for(dtype), f"call {call_no}: {name}")
-            assert torch.equal(a, b), f"call {call_no}: {name} differs from the regular entry point"
+            if same_kernel:   # same kernel, same arithmetic: bit for bit
+                assert torch.equal(a, b), f"call {call_no}: {name} differs from the regular entry point"
 
 
 def test_noalloc_refuses_oversized_problem():
