@@ -371,7 +371,8 @@ def run_secondary(op, args):
     out = {"metric": f"{op} fwd+bwd tokens/s", "value": tokens / ((fwd_ms + bwd_ms) * 1e-3), "unit": "tokens/s", "n_gpus": 1,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True,
            "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": name},
-           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, "gpu_launches": 2 * args.steps + (1 if op == "timex" else 0) * args.steps,
+           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, # wkv6state: chunked forward + its guarded general-shape twin, then forward rebuild, chunked backward and twin
+           "gpu_launches": (5 if op == "wkv6state" else 3 if op == "timex" else 2) * args.steps,
            "clocks": clocks.summary()}
     if not args.no_cpu_baseline:
         ct = _cpu_time(cpu)
