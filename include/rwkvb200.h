@@ -89,6 +89,17 @@ int rwkvb200_wkv5_backward(int dtype, int B, int T, int C, int H, const void* r,
                            const void* v, const float* w, const float* ww, const void* u,
                            const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
                            void* stream);
+/* The same backward with a caller-provided work buffer of rwkvb200_wkv5_scratch_bytes(B,T,C) bytes
+ * (16 per element; contents undefined afterwards).  No counterpart in the reference.  With it,
+ * bf16 / head size 64 / T a multiple of 16 runs on the chunked tensor-core kernels (RWKV-5 is
+ * RWKV-6 with a decay that is constant over time; they need the chunk-start states of a forward
+ * pass, which go into the buffer); other shapes, and decays too strong for the chunked form, run
+ * the same kernel as rwkvb200_wkv5_backward.  The forward takes the chunked path on its own. */
+size_t rwkvb200_wkv5_scratch_bytes(int B, int T, int C);
+int rwkvb200_wkv5_backward_ws(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                              const void* v, const float* w, const float* ww, const void* u,
+                              const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                              void* scratch, void* stream);
 
 /* ---------------------------------------------------------------------------------
  * RWKV-5a WKV (decay w1[j]*w2[i], bonus u1[j]+u2[i]), fp32 or bf16 activations.

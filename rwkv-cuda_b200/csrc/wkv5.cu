@@ -20,6 +20,9 @@
 // gw is returned multiplied by ww = -exp(w_raw), gw/gu as per-batch partials (B,C), exactly
 // what the reference kernels hand to their autograd wrappers.
 #include "common.cuh"
+#include "wkv6_chunked.cuh"
+#include <initializer_list>
+#include <type_traits>
 
 namespace rwkvb200 {
 namespace {
@@ -35,7 +38,8 @@ __global__ void __launch_bounds__(NMAX) wkv5_forward_kernel(int T, int C, int H,
                                                            const E* __restrict__ k_, const E* __restrict__ v_,
                                                            const float* __restrict__ w1_, const E* __restrict__ u1_,
                                                            const float* __restrict__ w2_, const E* __restrict__ u2_,
-                                                           E* __restrict__ y_) {
+                                                           E* __restrict__ y_, const int* __restrict__ only_if_) {
+    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernel's result stands
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks;
@@ -88,7 +92,8 @@ __global__ void __launch_bounds__(NMAX) wkv5_backward_kernel(
     const float* __restrict__ w1_, const float* __restrict__ ww1_, const E* __restrict__ u1_,
     const float* __restrict__ w2_, const float* __restrict__ ww2_, const E* __restrict__ u2_,
     const E* __restrict__ gy_, E* __restrict__ gr_, E* __restrict__ gk_, E* __restrict__ gv_, E* __restrict__ gw1_,
-    E* __restrict__ gu1_, E* __restrict__ gw2_, E* __restrict__ gu2_) {
+    E* __restrict__ gu1_, E* __restrict__ gw2_, E* __restrict__ gu2_, const int* __restrict__ only_if_) {
+    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernels' result stands
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks, vs, gs;
@@ -216,13 +221,31 @@ __global__ void __launch_bounds__(NMAX) wkv5_backward_kernel(
     }
 }
 
+template <typename E>
+bool chunked_ok(int T, int N, std::initializer_list<const void*> ps) {
+    if (!std::is_same<E, bf16>::value || N != 64 || T % 16 != 0) return false;
+    for (const void* p : ps)
+        if (p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) != 0) return false;
+    return true;
+}
+
 template <typename E, bool DUAL>
 int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const float* w1,
                const void* u1, const float* w2, const void* u2, void* y, cudaStream_t st) {
     const int N = C / H;
+    const int* only_if = nullptr;
+    if (!DUAL && chunked_ok<E>(T, N, {r, k, v, u1, y})) {
+        // RWKV-5 is RWKV-6 with a decay that does not change over time: the chunked tensor-core kernel
+        // runs first, the general-shape kernel below only if the decay is too strong for the chunked form
+        int* flag = wkv6_chunked_next_flag();
+        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "wkv5_forward: no device flag");
+        cudaMemsetAsync(flag, 0, sizeof(int), st);
+        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w1, 2, u1, nullptr, 0, y, nullptr, nullptr, flag, st)) return e;
+        only_if = flag;
+    }
 #define RWKV_GO(NM)                                                                                           \
     wkv5_forward_kernel<E, NM, DUAL><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, \
-                                                            w1, (const E*)u1, w2, (const E*)u2, (E*)y)
+                                                            w1, (const E*)u1, w2, (const E*)u2, (E*)y, only_if)
     switch (head_capacity(N)) {
         case 32: RWKV_GO(32); break;
         case 64: RWKV_GO(64); break;
@@ -235,12 +258,26 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
 template <typename E, bool DUAL>
 int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const float* w1,
                const float* ww1, const void* u1, const float* w2, const float* ww2, const void* u2, const void* gy,
-               void* gr, void* gk, void* gv, void* gw1, void* gu1, void* gw2, void* gu2, cudaStream_t st) {
+               void* gr, void* gk, void* gv, void* gw1, void* gu1, void* gw2, void* gu2, cudaStream_t st,
+               void* scratch = nullptr) {
     const int N = C / H;
+    const int* only_if = nullptr;
+    if (!DUAL && scratch != nullptr && chunked_ok<E>(T, N, {r, k, v, u1, gy, gr, gk, gv, gw1, gu1, scratch})) {
+        // chunked forward into the scratch buffer (chunk-start states), chunked reverse pass, then the
+        // general-shape kernel only if the decay is too strong for the chunked form
+        int* flag = wkv6_chunked_next_flag();
+        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "wkv5_backward: no device flag");
+        cudaMemsetAsync(flag, 0, sizeof(int), st);
+        float* ck = static_cast<float*>(scratch);
+        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
+        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, 1, st))
+            return e;
+        only_if = flag;
+    }
 #define RWKV_GO(NM)                                                                                              \
     wkv5_backward_kernel<E, NM, DUAL><<<B * H, NM, 0, st>>>(                                                     \
         T, C, H, N, (const E*)r, (const E*)k, (const E*)v, w1, ww1, (const E*)u1, w2, ww2, (const E*)u2,         \
-        (const E*)gy, (E*)gr, (E*)gk, (E*)gv, (E*)gw1, (E*)gu1, (E*)gw2, (E*)gu2)
+        (const E*)gy, (E*)gr, (E*)gk, (E*)gv, (E*)gw1, (E*)gu1, (E*)gw2, (E*)gu2, only_if)
     switch (head_capacity(N)) {
         case 32: RWKV_GO(32); break;
         case 64: RWKV_GO(64); break;
@@ -284,6 +321,26 @@ extern "C" int rwkvb200_wkv5_backward(int dtype, int B, int T, int C, int H, con
                                           gw, gu, nullptr, nullptr, as_stream(stream))
                : launch_bwd<bf16, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
                                          gw, gu, nullptr, nullptr, as_stream(stream));
+}
+
+extern "C" size_t rwkvb200_wkv5_scratch_bytes(int B, int T, int C) {
+    if (B <= 0 || T <= 0 || C <= 0) return 0;
+    return (size_t)B * T * C * sizeof(float) * 4;   // one fp32 64x64 state per 16 tokens and head
+}
+
+extern "C" int rwkvb200_wkv5_backward_ws(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                         const void* v, const float* w, const float* ww, const void* u,
+                                         const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                                         void* scratch, void* stream) {
+    if (int e = check_dims("wkv5_backward_ws", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(ww); RWKV_NOTNULL(u);
+    RWKV_NOTNULL(gy); RWKV_NOTNULL(gr); RWKV_NOTNULL(gk); RWKV_NOTNULL(gv); RWKV_NOTNULL(gw); RWKV_NOTNULL(gu);
+    RWKV_NOTNULL(scratch);
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
+                                          gw, gu, nullptr, nullptr, as_stream(stream), scratch)
+               : launch_bwd<bf16, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
+                                         gw, gu, nullptr, nullptr, as_stream(stream), scratch);
 }
 
 extern "C" int rwkvb200_wkv5a_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,

@@ -241,15 +241,6 @@ __global__ void __launch_bounds__(NMAX) wkv6_backward_kernel(
     }
 }
 
-// Flags of the chunked kernels ("a chunk's decay was too strong"): a small ring, one slot per call, so
-// that calls in flight on different streams do not share one.
-static __device__ int g_wkv6_unsafe[64];
-static int* next_flag() {
-    static int* base = nullptr;
-    static unsigned counter = 0;
-    if (base == nullptr && cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_wkv6_unsafe) != cudaSuccess) return nullptr;
-    return base + (counter++ & 63);
-}
 static int g_wkv6_chunked_enabled = 1;
 
 template <typename E>
@@ -268,7 +259,7 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
     if (chunked_ok<E>(T, N, {r, k, v, w, u, s0, y, sT})) {
         // tensor-core kernel first; the general-shape kernel below then only runs if that one found a
         // chunk whose decay is too strong for the chunked form
-        int* flag = next_flag();
+        int* flag = wkv6_chunked_next_flag();
         RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "%s: no device flag", what);
         cudaMemsetAsync(flag, 0, sizeof(int), st);
         if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, y, sT, nullptr, flag, st)) return e;
@@ -297,12 +288,12 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         // tensor-core kernels first: a forward pass that leaves the chunk-start states in the scratch
         // buffer, then the reverse pass; the general-shape kernel below then only runs if a chunk's decay
         // was too strong for the chunked form (it reuses the front of the same scratch buffer)
-        int* flag = next_flag();
+        int* flag = wkv6_chunked_next_flag();
         RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "%s: no device flag", what);
         cudaMemsetAsync(flag, 0, sizeof(int), st);
         float* ck = static_cast<float*>(scratch);
         if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
-        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
+        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, 0, st))
             return e;
         only_if = flag;
     }

@@ -38,6 +38,15 @@ struct FSmem {                                                       // floats
     static constexpr int kBytes = kEnd * 4;
 };
 
+// log2 of the decay of one (token, channel): w_mode 0 = fp32 log-decay (B,T,C), 1 = bf16 raw input
+// (B,T,C), log-decay = -exp(w); static per channel (RWKV-5): 2 = fp32 decay value (C), 3 = fp32 log-decay (C)
+__device__ __forceinline__ float decay_log2(const void* w, int mode, i64 tok_idx, int ch_idx) {
+    if (mode == 0) return reinterpret_cast<const float*>(w)[tok_idx] * 1.4426950408889634f;
+    if (mode == 1) return -fexp(__bfloat162float(reinterpret_cast<const bf16*>(w)[tok_idx])) * 1.4426950408889634f;
+    if (mode == 2) return __log2f(reinterpret_cast<const float*>(w)[ch_idx]);
+    return reinterpret_cast<const float*>(w)[ch_idx] * 1.4426950408889634f;
+}
+
 __device__ __forceinline__ float load_s0(const void* p, int kind, i64 idx) {
     if (kind == 2) return reinterpret_cast<const float*>(p)[idx];
     if (kind == 1) return __bfloat162float(reinterpret_cast<const bf16*>(p)[idx]);
@@ -46,7 +55,7 @@ __device__ __forceinline__ float load_s0(const void* p, int kind, i64 idx) {
 
 __global__ void __launch_bounds__(NT, 4)
 wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ k_,
-                     const bf16* __restrict__ v_, const void* __restrict__ w_, int w_raw, const bf16* __restrict__ u_,
+                     const bf16* __restrict__ v_, const void* __restrict__ w_, int w_mode, const bf16* __restrict__ u_,
                      const void* __restrict__ s0_, int s0_kind, bf16* __restrict__ y_, float* __restrict__ sT_,
                      float* __restrict__ ck_, int* __restrict__ unsafe_) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -89,8 +98,7 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             const i64 o = tok0 + (i64)(c * L + pt0 + q) * C + pj;
-            ld[q] = w_raw ? -fexp(__bfloat162float(reinterpret_cast<const bf16*>(w_)[o])) * 1.4426950408889634f
-                          : reinterpret_cast<const float*>(w_)[o] * 1.4426950408889634f;
+            ld[q] = decay_log2(w_, w_mode, o, hh * N + pj);
         }
     };
     issue_loads(0, 0);
@@ -251,10 +259,10 @@ __device__ __forceinline__ void store_ds0(void* p, int kind, i64 idx, float x) {
 
 __global__ void __launch_bounds__(NT, 2)
 wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ k_,
-                      const bf16* __restrict__ v_, const void* __restrict__ w_, int w_raw, const bf16* __restrict__ u_,
+                      const bf16* __restrict__ v_, const void* __restrict__ w_, int w_mode, const bf16* __restrict__ u_,
                       const bf16* __restrict__ gy_, const float* __restrict__ dsT_, const float* __restrict__ ck_,
                       bf16* __restrict__ gr_, bf16* __restrict__ gk_, bf16* __restrict__ gv_, bf16* __restrict__ gw_,
-                      bf16* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind) {
+                      bf16* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind, int gw_reduce) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* sm = reinterpret_cast<float*>(smem_raw);
     bf16* raw = reinterpret_cast<bf16*>(smem_raw);
@@ -285,7 +293,7 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             ET[nt][e] = dsT_ ? dsT_[sbase + col * N + row] : 0.f;
         }
     const float u0 = __bfloat162float(u_[hh * N + row0 + g]), u1 = __bfloat162float(u_[hh * N + row0 + g + 8]);
-    float gu_acc[2] = {0.f, 0.f};
+    float gu_acc[2] = {0.f, 0.f}, gw_acc[2] = {0.f, 0.f};   // per-batch sums over time (gw only for a static decay)
 
     const int lrow = tid >> 3, lseg = tid & 7;
     auto issue_raw = [&](int c, int stage) {
@@ -310,8 +318,7 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             const i64 o = tok0 + (i64)(c * L + pt0 + q) * C + pj;
-            ld[q] = w_raw ? -fexp(__bfloat162float(reinterpret_cast<const bf16*>(w_)[o])) * 1.4426950408889634f
-                          : reinterpret_cast<const float*>(w_)[o] * 1.4426950408889634f;
+            ld[q] = decay_log2(w_, w_mode, o, hh * N + pj);
         }
     };
     issue_raw(nchunks - 1, (nchunks - 1) & 1);
@@ -520,7 +527,8 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             for (int q = 0; q < 4; ++q) {
                 const int nt = q >> 1, e = e0 + (q & 1), tt = nt * 8 + 2 * t + (q & 1);
                 const float Gd = A0[h2] - pre[q] - rdr[nt][e];
-                gw_[tok0 + (i64)(c * L + tt) * C + j] = __float2bfloat16_rn(Gd * lw[nt][e]);
+                if (gw_reduce) gw_acc[h2] = fmaf(Gd, lw[nt][e], gw_acc[h2]);
+                else gw_[tok0 + (i64)(c * L + tt) * C + j] = __float2bfloat16_rn(Gd * lw[nt][e]);
             }
         }
     }
@@ -531,6 +539,11 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         gu_acc[h2] += __shfl_xor_sync(0xffffffffu, gu_acc[h2], 1);
         gu_acc[h2] += __shfl_xor_sync(0xffffffffu, gu_acc[h2], 2);
         if (t == 0) gu_[(i64)bb * C + hh * N + row0 + g + h2 * 8] = __float2bfloat16_rn(gu_acc[h2]);
+        if (gw_reduce) {
+            gw_acc[h2] += __shfl_xor_sync(0xffffffffu, gw_acc[h2], 1);
+            gw_acc[h2] += __shfl_xor_sync(0xffffffffu, gw_acc[h2], 2);
+            if (t == 0) gw_[(i64)bb * C + hh * N + row0 + g + h2 * 8] = __float2bfloat16_rn(gw_acc[h2]);
+        }
     }
     if (ds0_kind != 0) {
 #pragma unroll
@@ -543,29 +556,40 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
 }  // namespace v6c
 
-int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
+// Flags of the chunked kernels ("a chunk's decay was too strong"): a small ring, one slot per call, so
+// that calls in flight on different streams do not share one.
+static __device__ int g_chunked_unsafe[64];
+int* wkv6_chunked_next_flag() {
+    static int* base = nullptr;
+    static unsigned counter = 0;
+    if (base == nullptr && cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_chunked_unsafe) != cudaSuccess) return nullptr;
+    return base + (counter++ & 63);
+}
+
+int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                          const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
                          cudaStream_t st) {
     using namespace v6c;
     cudaError_t e = cudaFuncSetAttribute(wkv6c_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FSmem::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     dim3 grid(H, B);
-    wkv6c_forward_kernel<<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, w_raw,
+    wkv6c_forward_kernel<<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, w_mode,
                                                           (const bf16*)u, s0, s0_kind, (bf16*)y, sT, ck, unsafe);
     return check_launch("wkv6_forward(chunked)");
 }
 
-int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
+int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                           const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
-                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st) {
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, int gw_reduce, cudaStream_t st) {
     using namespace v6c;
     static_assert(BSmem::kBytes <= 113 * 1024, "backward shared memory must allow 2 CTAs per SM");
     cudaError_t e = cudaFuncSetAttribute(wkv6c_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BSmem::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_backward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     dim3 grid(H, B);
-    wkv6c_backward_kernel<<<grid, NT, BSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, w_raw,
+    wkv6c_backward_kernel<<<grid, NT, BSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, w_mode,
                                                            (const bf16*)u, (const bf16*)gy, dsT, ck, (bf16*)gr,
-                                                           (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0, ds0_kind);
+                                                           (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0, ds0_kind,
+                                                           gw_reduce);
     return check_launch("wkv6_backward(chunked)");
 }
 

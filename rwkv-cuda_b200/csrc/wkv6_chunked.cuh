@@ -4,18 +4,23 @@
 
 namespace rwkvb200 {
 
-// s0_kind: 0 none, 1 bf16, 2 fp32 (one N x N block per (batch, head), [value][key]).  w: fp32
-// log-decay (w_raw = 0) or bf16 raw decay input (w_raw = 1, log-decay = -exp(w)).  ck: optional
+// s0_kind: 0 none, 1 bf16, 2 fp32 (one N x N block per (batch, head), [value][key]).  w_mode: 0 = fp32
+// log-decay (B,T,C), 1 = bf16 raw decay input (B,T,C), log-decay = -exp(w); static per channel
+// (RWKV-5): 2 = fp32 decay value (C), 3 = fp32 log-decay (C).  ck: optional
 // fp32 (B,H,T/16,N,N) chunk-start states.  unsafe: device flag raised when a chunk's cumulative
 // decay is too strong for the chunked form (the results are then invalid).
-int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
+int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                          const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
                          cudaStream_t st);
 
 // Backward; ck are the chunk-start states written by wkv6_chunked_forward on the same inputs
 // (fp32, (B,H,T/16,N,N)).  ds0_kind as s0_kind (0: no state gradient out).  gu is per batch: (B,C).
-int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_raw,
+int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                           const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
-                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st);
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, int gw_reduce, cudaStream_t st);
+// gw_reduce: gw is summed over time into (B,C) (static decay) instead of written per token.
+
+// one slot of a ring of device flags for `unsafe` (clear it in the stream before the forward)
+int* wkv6_chunked_next_flag();
 
 }  // namespace rwkvb200

@@ -128,9 +128,10 @@ def wkv5_backward(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu):
                        (gv, B * T * C, "gv"), (gw, B * C, "gw"), (gu, B * C, "gu")):
         _numel(t, n, name)
     with _dev(r, "r"):
-        call("rwkvb200_wkv5_backward", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
+        sc = scratch(_lib.lib().rwkvb200_wkv5_scratch_bytes(B, T, C), r.device)
+        call("rwkvb200_wkv5_backward_ws", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
              _ptr(w, "w", torch.float32), _ptr(ww, "ww", torch.float32),
-             *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), _stream(r))
+             *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), sc.data_ptr(), _stream(r))
 
 
 # ---- RWKV-5a (wkv5a/cuda/wkv5a_op.cpp:9-17) -------------------------------------------

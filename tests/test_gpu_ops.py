@@ -141,7 +141,7 @@ def test_wkv5_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,H,N", [(2, 96, 2, 64), (1, 40, 2, 128), (2, 33, 3, 17), (3, 5, 2, 4), (2, 70, 1, 32)])
+@pytest.mark.parametrize("B,T,H,N", [(2, 96, 2, 64), (2, 256, 3, 64), (1, 40, 2, 128), (2, 33, 3, 17), (3, 5, 2, 4), (2, 70, 1, 32)])
 def test_wkv5_oracle(R, dtype, B, T, H, N):
     g = Hh.gen(42)
     C = H * N
@@ -154,6 +154,26 @@ def test_wkv5_oracle(R, dtype, B, T, H, N):
     wants = [yo.detach()] + [x.grad for x in xs]
     for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu")):
         Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv5 {name}")
+
+
+def test_wkv5_strong_decay_falls_back(R):
+    """bf16, N = 64, T a multiple of 16 takes the chunked tensor-core kernels; with log-decays below
+    -5 per token (w_raw above 1.6) a chunk's cumulative decay is too small to divide by, and the
+    general-shape kernels must redo the call."""
+    B, T, H, N = 2, 64, 2, 64
+    dtype = torch.bfloat16
+    g = Hh.gen(3)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.rand(g, H, N, lo=-1, hi=2.5), Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv5(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv5(R, dtype, H, r, k, v, w_raw, u, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu")):
+        assert torch.isfinite(got.float()).all(), name
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv5 strong decay {name}")
 
 
 def run_wkv5a(R, dtype, H, r, k, v, w1, u1, w2, u2, gy):
