@@ -330,7 +330,7 @@ def run_secondary(op, args):
             O.wkv5(*xs, H).backward(gy[:1, :Tc].float().cpu())
         cpu_tokens, cpu_sample = Tc, f"B1 T{Tc} C{C} N{N} fp32 recurrent formula + autograd"
     elif op == "wkv6state":  # config 4: RWKV-6 with fp32 state in/out, bf16, B16 T4096 C4096 N64
-        B, T, H, N = 16, 4096, 64, 64
+        B, T, H, N = args.batch or 16, args.seq or 4096, 64, 64   # --batch/--seq: reduced case for profiler captures
         C = H * N
         name, dtype, tokens = f"wkv6state(_ex) fwd+bwd bf16 B{B} T{T} C{C} N{N}", "bf16", B * T
         r, k, v = ((0.5 * rn(B, T, C)).to(bf) for _ in range(3))
@@ -371,8 +371,8 @@ def run_secondary(op, args):
     out = {"metric": f"{op} fwd+bwd tokens/s", "value": tokens / ((fwd_ms + bwd_ms) * 1e-3), "unit": "tokens/s", "n_gpus": 1,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True,
            "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": name},
-           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, # wkv6state: chunked forward + its guarded general-shape twin, then forward rebuild, chunked backward and twin
-           "gpu_launches": (5 if op == "wkv6state" else 3 if op == "timex" else 2) * args.steps,
+           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, # wkv6state, wkv5: chunked forward + its guarded general-shape twin, then forward rebuild, chunked backward and twin
+           "gpu_launches": (5 if op in ("wkv6state", "wkv5") else 3 if op == "timex" else 2) * args.steps,
            "clocks": clocks.summary()}
     if not args.no_cpu_baseline:
         ct = _cpu_time(cpu)

@@ -270,7 +270,7 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         cudaMemsetAsync(flag, 0, sizeof(int), st);
         float* ck = static_cast<float*>(scratch);
         if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
-        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, 1, st))
+        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st))
             return e;
         only_if = flag;
     }

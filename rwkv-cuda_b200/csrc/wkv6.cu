@@ -293,7 +293,7 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         cudaMemsetAsync(flag, 0, sizeof(int), st);
         float* ck = static_cast<float*>(scratch);
         if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
-        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, 0, st))
+        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
             return e;
         only_if = flag;
     }

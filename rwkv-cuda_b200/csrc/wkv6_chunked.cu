@@ -38,13 +38,29 @@ struct FSmem {                                                       // floats
     static constexpr int kBytes = kEnd * 4;
 };
 
-// log2 of the decay of one (token, channel): w_mode 0 = fp32 log-decay (B,T,C), 1 = bf16 raw input
-// (B,T,C), log-decay = -exp(w); static per channel (RWKV-5): 2 = fp32 decay value (C), 3 = fp32 log-decay (C)
-__device__ __forceinline__ float decay_log2(const void* w, int mode, i64 tok_idx, int ch_idx) {
-    if (mode == 0) return reinterpret_cast<const float*>(w)[tok_idx] * 1.4426950408889634f;
-    if (mode == 1) return -fexp(__bfloat162float(reinterpret_cast<const bf16*>(w)[tok_idx])) * 1.4426950408889634f;
-    if (mode == 2) return __log2f(reinterpret_cast<const float*>(w)[ch_idx]);
-    return reinterpret_cast<const float*>(w)[ch_idx] * 1.4426950408889634f;
+// The decay input of one (token, channel), fetched one chunk ahead as raw bits and turned into the
+// log2 of the decay only where it is used (arithmetic right behind the load would make the warp wait
+// for it).  w_mode 0 = fp32 log-decay (B,T,C), 1 = bf16 raw input (B,T,C), log-decay = -exp(w);
+// static per channel (RWKV-5): 2 = fp32 decay value (C), 3 = fp32 log-decay (C).
+// (volatile asm: the compiler must issue the load here, not sink it to the first use a chunk later)
+template <int mode>
+__device__ __forceinline__ uint32_t decay_bits(const void* w, i64 tok_idx, int ch_idx) {
+    uint32_t x;
+    if (mode == 1) {
+        unsigned short h;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(h) : "l"(reinterpret_cast<const unsigned short*>(w) + tok_idx));
+        x = (uint32_t)h << 16;
+    } else {
+        asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(x) : "l"(reinterpret_cast<const uint32_t*>(w) + (mode == 0 ? tok_idx : (i64)ch_idx)));
+    }
+    return x;
+}
+template <int mode>
+__device__ __forceinline__ float decay_log2(uint32_t bits) {
+    const float x = __uint_as_float(bits);
+    if (mode == 1) return -fexp(x) * 1.4426950408889634f;
+    if (mode == 2) return __log2f(x);
+    return x * 1.4426950408889634f;
 }
 
 __device__ __forceinline__ float load_s0(const void* p, int kind, i64 idx) {
@@ -53,9 +69,10 @@ __device__ __forceinline__ float load_s0(const void* p, int kind, i64 idx) {
     return 0.f;
 }
 
+template <int WMODE>
 __global__ void __launch_bounds__(NT, 4)
 wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ k_,
-                     const bf16* __restrict__ v_, const void* __restrict__ w_, int w_mode, const bf16* __restrict__ u_,
+                     const bf16* __restrict__ v_, const void* __restrict__ w_, const bf16* __restrict__ u_,
                      const void* __restrict__ s0_, int s0_kind, bf16* __restrict__ y_, float* __restrict__ sT_,
                      float* __restrict__ ck_, int* __restrict__ unsafe_) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -93,13 +110,10 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
     // global memory, one chunk ahead, in log2 units
     const int pj = tid & 63, phf = tid >> 6, pt0 = phf * 8;
     const float pu = __bfloat162float(u_[hh * N + pj]);
-    float ld[8];
+    uint32_t ldb[8];
     auto fetch_decay = [&](int c) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const i64 o = tok0 + (i64)(c * L + pt0 + q) * C + pj;
-            ld[q] = decay_log2(w_, w_mode, o, hh * N + pj);
-        }
+        for (int q = 0; q < 8; ++q) ldb[q] = decay_bits<WMODE>(w_, tok0 + (i64)(c * L + pt0 + q) * C + pj, hh * N + pj);
     };
     issue_loads(0, 0);
     fetch_decay(0);
@@ -118,7 +132,7 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
             float cs[8];
             float run = 0.f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) { run += ld[q]; cs[q] = run; }
+            for (int q = 0; q < 8; ++q) { run += decay_log2<WMODE>(ldb[q]); cs[q] = run; }
             Hs[phf * N + pj] = run;
             float xr[8], xk[8], xv[8];
 #pragma unroll
@@ -257,12 +271,14 @@ __device__ __forceinline__ void store_ds0(void* p, int kind, i64 idx, float x) {
     else if (kind == 1) reinterpret_cast<bf16*>(p)[idx] = __float2bfloat16_rn(x);
 }
 
+template <int WMODE>
 __global__ void __launch_bounds__(NT, 2)
 wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ k_,
-                      const bf16* __restrict__ v_, const void* __restrict__ w_, int w_mode, const bf16* __restrict__ u_,
+                      const bf16* __restrict__ v_, const void* __restrict__ w_, const bf16* __restrict__ u_,
                       const bf16* __restrict__ gy_, const float* __restrict__ dsT_, const float* __restrict__ ck_,
                       bf16* __restrict__ gr_, bf16* __restrict__ gk_, bf16* __restrict__ gv_, bf16* __restrict__ gw_,
-                      bf16* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind, int gw_reduce) {
+                      bf16* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind) {
+    constexpr bool gw_reduce = WMODE >= 2;   // a static decay has one gradient per channel and batch row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* sm = reinterpret_cast<float*>(smem_raw);
     bf16* raw = reinterpret_cast<bf16*>(smem_raw);
@@ -313,13 +329,10 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     };
     const int pj = tid & 63, phf = tid >> 6, pt0 = phf * 8;
     const float pu = __bfloat162float(u_[hh * N + pj]);
-    float ld[8];   // log2-unit log-decays of this thread's (channel, 8 tokens) of the next chunk
+    uint32_t ldb[8];   // decay inputs of this thread's (channel, 8 tokens) of the next chunk
     auto fetch_decay = [&](int c) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const i64 o = tok0 + (i64)(c * L + pt0 + q) * C + pj;
-            ld[q] = decay_log2(w_, w_mode, o, hh * N + pj);
-        }
+        for (int q = 0; q < 8; ++q) ldb[q] = decay_bits<WMODE>(w_, tok0 + (i64)(c * L + pt0 + q) * C + pj, hh * N + pj);
     };
     issue_raw(nchunks - 1, (nchunks - 1) & 1);
     issue_state(nchunks - 1);
@@ -338,10 +351,10 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
         // ---- prep: thread = (channel, half of the chunk) ----------------------------------------
         {
-            float cs[8];
+            float cs[8], ld[8];
             float run = 0.f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) { run += ld[q]; cs[q] = run; }
+            for (int q = 0; q < 8; ++q) { ld[q] = decay_log2<WMODE>(ldb[q]); run += ld[q]; cs[q] = run; }
             float xr[8], xk[8], xv[8], xd[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -570,26 +583,50 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
                          const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
                          cudaStream_t st) {
     using namespace v6c;
-    cudaError_t e = cudaFuncSetAttribute(wkv6c_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FSmem::kBytes);
-    RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_forward(chunked): decay mode %d", w_mode);
     dim3 grid(H, B);
-    wkv6c_forward_kernel<<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, w_mode,
-                                                          (const bf16*)u, s0, s0_kind, (bf16*)y, sT, ck, unsafe);
+#define RWKV_GO(M)                                                                                                     \
+    do {                                                                                                               \
+        cudaError_t e = cudaFuncSetAttribute(wkv6c_forward_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                             FSmem::kBytes);                                                           \
+        RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        wkv6c_forward_kernel<M><<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, \
+                                                                 (const bf16*)u, s0, s0_kind, (bf16*)y, sT, ck, unsafe); \
+    } while (0)
+    switch (w_mode) {
+        case 0: RWKV_GO(0); break;
+        case 1: RWKV_GO(1); break;
+        case 2: RWKV_GO(2); break;
+        default: RWKV_GO(3); break;
+    }
+#undef RWKV_GO
     return check_launch("wkv6_forward(chunked)");
 }
 
 int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                           const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
-                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, int gw_reduce, cudaStream_t st) {
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st) {
     using namespace v6c;
     static_assert(BSmem::kBytes <= 113 * 1024, "backward shared memory must allow 2 CTAs per SM");
-    cudaError_t e = cudaFuncSetAttribute(wkv6c_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BSmem::kBytes);
-    RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_backward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_backward(chunked): decay mode %d", w_mode);
     dim3 grid(H, B);
-    wkv6c_backward_kernel<<<grid, NT, BSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, w_mode,
-                                                           (const bf16*)u, (const bf16*)gy, dsT, ck, (bf16*)gr,
-                                                           (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0, ds0_kind,
-                                                           gw_reduce);
+#define RWKV_GO(M)                                                                                                      \
+    do {                                                                                                                \
+        cudaError_t e = cudaFuncSetAttribute(wkv6c_backward_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                             BSmem::kBytes);                                                            \
+        RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_backward: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        wkv6c_backward_kernel<M><<<grid, NT, BSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, \
+                                                                  (const bf16*)u, (const bf16*)gy, dsT, ck, (bf16*)gr,  \
+                                                                  (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0,      \
+                                                                  ds0_kind);                                            \
+    } while (0)
+    switch (w_mode) {
+        case 0: RWKV_GO(0); break;
+        case 1: RWKV_GO(1); break;
+        case 2: RWKV_GO(2); break;
+        default: RWKV_GO(3); break;
+    }
+#undef RWKV_GO
     return check_launch("wkv6_backward(chunked)");
 }
 

@@ -17,8 +17,8 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
 // (fp32, (B,H,T/16,N,N)).  ds0_kind as s0_kind (0: no state gradient out).  gu is per batch: (B,C).
 int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                           const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
-                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, int gw_reduce, cudaStream_t st);
-// gw_reduce: gw is summed over time into (B,C) (static decay) instead of written per token.
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st);
+// With a static decay (w_mode 2, 3) gw is summed over time into (B,C) instead of written per token.
 
 // one slot of a ring of device flags for `unsafe` (clear it in the stream before the forward)
 int* wkv6_chunked_next_flag();
