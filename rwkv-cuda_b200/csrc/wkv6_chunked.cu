@@ -69,7 +69,8 @@ __device__ __forceinline__ float load_s0(const void* p, int kind, i64 idx) {
     return 0.f;
 }
 
-template <int WMODE>
+// STATES_ONLY: the pass of the backward that only rebuilds the chunk-start states (no r, no A, no y).
+template <int WMODE, bool STATES_ONLY>
 __global__ void __launch_bounds__(NT, 4)
 wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ k_,
                      const bf16* __restrict__ v_, const void* __restrict__ w_, const bf16* __restrict__ u_,
@@ -103,7 +104,7 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
     auto issue_loads = [&](int c, int stage) {
         const i64 off = tok0 + (i64)(c * L + lrow) * C + lseg * 8;
 #pragma unroll
-        for (int x = 0; x < 3; ++x) cp_async16(raw + ((stage * 3 + x) * L + lrow) * N + lseg * 8, src[x] + off);
+        for (int x = STATES_ONLY ? 1 : 0; x < 3; ++x) cp_async16(raw + ((stage * 3 + x) * L + lrow) * N + lseg * 8, src[x] + off);
         cp_async_commit();
     };
     // thread = (channel j, half of the chunk) in the preparation; its log-decays come straight from
@@ -137,7 +138,8 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
             float xr[8], xk[8], xv[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                xr[q] = to_f(R[(pt0 + q) * N + pj]); xk[q] = to_f(K[(pt0 + q) * N + pj]); xv[q] = to_f(V[(pt0 + q) * N + pj]);
+                xr[q] = STATES_ONLY ? 0.f : to_f(R[(pt0 + q) * N + pj]);
+                xk[q] = to_f(K[(pt0 + q) * N + pj]); xv[q] = to_f(V[(pt0 + q) * N + pj]);
             }
             __syncthreads();
             const float base = phf ? Hs[pj] : 0.f;
@@ -153,11 +155,13 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
                 const int tt = pt0 + q;
                 const float lam = base + cs[q];
                 const float p = fex2(lam), ip = fex2(-lam);
-                Rt[tt * PK + jp] = tf32rf(xr[q] * pprev);
                 Kt[tt * PK + jp] = tf32rf(xk[q] * ip);
                 Vf[tt * PK + jp] = xv[q];
-                Ru[tt * PK + jp] = tf32rf(xr[q] * pu);
-                Kr[tt * PK + jp] = xk[q];
+                if (!STATES_ONLY) {
+                    Rt[tt * PK + jp] = tf32rf(xr[q] * pprev);
+                    Ru[tt * PK + jp] = tf32rf(xr[q] * pu);
+                    Kr[tt * PK + jp] = xk[q];
+                }
                 pprev = p;
             }
         }
@@ -165,7 +169,7 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
         if (c + 1 < nchunks) fetch_decay(c + 1);
 
         // ---- A: warp 0 the strict part k~_s.r~_t, warp 1 the diagonal sum_j r u k; stored [t][s] ----
-        if (warp < 2) {
+        if (!STATES_ONLY && warp < 2) {
             const float* Am = warp ? Kr : Kt;
             const float* Bm = warp ? Ru : Rt;
             uint32_t areg[8][4];
@@ -185,7 +189,7 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
         // ---- X = S0 R~ --------------------------------------------------------------------------
         float X[2][4] = {};
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < (STATES_ONLY ? 0 : 8); ++ks) {
             const uint32_t a0 = tf32r(S[ks][0]), a1 = tf32r(S[ks][2]), a2 = tf32r(S[ks][1]), a3 = tf32r(S[ks][3]);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
@@ -201,12 +205,12 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
                 *reinterpret_cast<float2*>(dst + (row0 + g + 8) * N + nt * 8 + 2 * t) = make_float2(S[nt][2], S[nt][3]);
             }
         }
-        __syncthreads();
+        if (!STATES_ONLY) __syncthreads();
 
         // ---- Y = X + V A;  S = (S + V K~) diag(We) ------------------------------------------------
         uint32_t vreg[2][4];
         load_a_kperm<2>(vreg, Vf, PK, row0, g, t);           // A[m=i][k=s] = v_s[i]
-        gemm_rs<2, 2>(X, vreg, AT, PU, g, t);                // (B[k=s][n=t] = A[s][t])
+        if (!STATES_ONLY) gemm_rs<2, 2>(X, vreg, AT, PU, g, t);   // (B[k=s][n=t] = A[s][t])
         gemm_rs_kperm<8, 2>(S, vreg, Kt, PK, g, t);           // (B[k=t][n=j] = k~_t[j])
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
@@ -218,7 +222,7 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = row0 + g + ((e & 2) ? 8 : 0), tt = nt * 8 + 2 * t + (e & 1);
-                if (y_ != nullptr) y_[tok0 + (i64)(c * L + tt) * C + i] = __float2bfloat16_rn(X[nt][e]);
+                if (!STATES_ONLY) y_[tok0 + (i64)(c * L + tt) * C + i] = __float2bfloat16_rn(X[nt][e]);
             }
     }
 
@@ -585,13 +589,19 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
     using namespace v6c;
     RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_forward(chunked): decay mode %d", w_mode);
     dim3 grid(H, B);
-#define RWKV_GO(M)                                                                                                     \
+#define RWKV_GO1(M, SO)                                                                                                \
     do {                                                                                                               \
-        cudaError_t e = cudaFuncSetAttribute(wkv6c_forward_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+        cudaError_t e = cudaFuncSetAttribute(wkv6c_forward_kernel<M, SO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              FSmem::kBytes);                                                           \
         RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        wkv6c_forward_kernel<M><<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, \
-                                                                 (const bf16*)u, s0, s0_kind, (bf16*)y, sT, ck, unsafe); \
+        wkv6c_forward_kernel<M, SO><<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, \
+                                                                     w, (const bf16*)u, s0, s0_kind, (bf16*)y, sT, ck,  \
+                                                                     unsafe);                                          \
+    } while (0)
+#define RWKV_GO(M)                    \
+    do {                              \
+        if (y == nullptr) RWKV_GO1(M, true); \
+        else RWKV_GO1(M, false);      \
     } while (0)
     switch (w_mode) {
         case 0: RWKV_GO(0); break;
@@ -600,6 +610,7 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
         default: RWKV_GO(3); break;
     }
 #undef RWKV_GO
+#undef RWKV_GO1
     return check_launch("wkv6_forward(chunked)");
 }
 

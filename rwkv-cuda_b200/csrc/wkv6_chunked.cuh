@@ -6,7 +6,7 @@ namespace rwkvb200 {
 
 // s0_kind: 0 none, 1 bf16, 2 fp32 (one N x N block per (batch, head), [value][key]).  w_mode: 0 = fp32
 // log-decay (B,T,C), 1 = bf16 raw decay input (B,T,C), log-decay = -exp(w); static per channel
-// (RWKV-5): 2 = fp32 decay value (C), 3 = fp32 log-decay (C).  ck: optional
+// (RWKV-5): 2 = fp32 decay value (C), 3 = fp32 log-decay (C).  y = NULL: only the states are rebuilt.  ck: optional
 // fp32 (B,H,T/16,N,N) chunk-start states.  unsafe: device flag raised when a chunk's cumulative
 // decay is too strong for the chunked form (the results are then invalid).
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
