@@ -16,6 +16,7 @@
 // same problem (it starts by reading the flag, and returns at once when the flag is clear).
 #include "wkv7_chunked.cuh"
 #include "wkv6_chunked.cuh"
+#include <atomic>
 
 namespace rwkvb200 {
 namespace v6c {
@@ -577,10 +578,17 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 // that calls in flight on different streams do not share one.
 static __device__ int g_chunked_unsafe[64];
 int* wkv6_chunked_next_flag() {
-    static int* base = nullptr;
-    static unsigned counter = 0;
-    if (base == nullptr && cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_chunked_unsafe) != cudaSuccess) return nullptr;
-    return base + (counter++ & 63);
+    constexpr int kMaxDevices = 64;
+    static int* base[kMaxDevices] = {};             // device address of the ring, per device
+    static std::atomic<unsigned> counter{0};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (base[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_chunked_unsafe) != cudaSuccess) return nullptr;
+        base[dev] = static_cast<int*>(p);
+    }
+    return base[dev] + (counter.fetch_add(1) & 63);
 }
 
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
