@@ -310,10 +310,12 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int row = row0 + g + ((e & 2) ? 8 : 0), col = nt * 8 + 2 * t + (e & 1);
-            E[nt][e] = dsT_ ? dsT_[sbase + row * N + col] : 0.f;
-            ET[nt][e] = dsT_ ? dsT_[sbase + col * N + row] : 0.f;
+            E[nt][e] = dsT_ ? dsT_[sbase + row * N + key_real(col)] : 0.f;      // E columns: logical key index
+            ET[nt][e] = dsT_ ? dsT_[sbase + col * N + key_real(row)] : 0.f;    // ET rows: logical key index
         }
-    const float u0 = __bfloat162float(u_[hh * N + row0 + g]), u1 = __bfloat162float(u_[hh * N + row0 + g + 8]);
+    // fragment rows (g, g+8) are the adjacent real key channels (2g, 2g+1) (key_logical / key_real)
+    const float2 u01 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(u_ + hh * N + row0 + 2 * g));
+    const float u0 = u01.x, u1 = u01.y;
     float gu_acc[2] = {0.f, 0.f}, gw_acc[2] = {0.f, 0.f};   // per-batch sums over time (gw only for a static decay)
 
     const int lrow = tid >> 3, lseg = tid & 7;
@@ -369,8 +371,10 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             Hs[phf * N + pj] = run;
             __syncthreads();
             const float base = phf ? Hs[pj] : 0.f;
-            if (phf == 0) We[pj] = fex2(Hs[pj] + Hs[N + pj]);
-            const int jp = (pj & ~7) + perm8(pj & 7);
+            const int jl = key_logical(pj);
+            if (phf == 0) We[jl] = fex2(Hs[pj] + Hs[N + pj]);
+            const int jp = (jl & ~7) + perm8(jl & 7);     // key-indexed arrays: logical order
+            const int vp = (pj & ~7) + perm8(pj & 7);     // value-indexed arrays (v, gy): natural order
             float pprev = phf ? fex2(base) : 1.f;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -379,8 +383,8 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 const float p = fex2(lam), ip = fex2(-lam);
                 Rt[tt * PK + jp] = tf32rf(xr[q] * pprev);
                 Kt[tt * PK + jp] = tf32rf(xk[q] * ip);
-                Vf[tt * PK + jp] = xv[q];
-                dYf[tt * PK + jp] = xd[q];
+                Vf[tt * PK + vp] = xv[q];
+                dYf[tt * PK + vp] = xd[q];
                 Ru[tt * PK + jp] = tf32rf(xr[q] * pu);
                 Kr[tt * PK + jp] = xk[q];
                 Pt[tt * PK + pj] = p;
@@ -456,8 +460,9 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             const uint32_t a0 = tf32r(ET[ks][0]), a1 = tf32r(ET[ks][2]), a2 = tf32r(ET[ks][1]), a3 = tf32r(ET[ks][3]);
-            const float* p0 = S0 + (ks * 8 + 2 * t) * PS0 + row0 + g;   // A[m=j][k=i] = S0[i][j]
-            const uint32_t s0a = tf32r(p0[0]), s1a = tf32r(p0[8]), s2a = tf32r(p0[PS0]), s3a = tf32r(p0[PS0 + 8]);
+            const float* p0 = S0 + (ks * 8 + 2 * t) * PS0 + row0 + 2 * g;   // A[m=j][k=i] = S0[i][j], rows (g, g+8) = real (2g, 2g+1)
+            const float2 sx = *reinterpret_cast<const float2*>(p0), sy = *reinterpret_cast<const float2*>(p0 + PS0);
+            const uint32_t s0a = tf32r(sx.x), s1a = tf32r(sx.y), s2a = tf32r(sy.x), s3a = tf32r(sy.y);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const float* pv = Vf + (nt * 8 + g) * PK + ks * 8 + t;
@@ -472,16 +477,25 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         {
             uint32_t rtlo[2][4], kthi[2][4], ktlo[2][4];
 #pragma unroll
-            for (int ks = 0; ks < 2; ++ks)
+            for (int ks = 0; ks < 2; ++ks) {
+                float2 pp2 = make_float2(1.f, 1.f);
+                if (ks > 0 || t > 0) pp2 = *reinterpret_cast<const float2*>(Pt + (ks * 8 + 2 * t - 1) * PK + row0 + 2 * g);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int u = ks * 8 + 2 * t + (e >> 1), j = row0 + g + (e & 1) * 8;
-                    const float pu_ = Pt[u * PK + j];
-                    const float pp = u > 0 ? Pt[(u - 1) * PK + j] : 1.f;
-                    const float xr = to_f(R[u * RP + j]) * pp, xk = to_f(K[u * RP + j]) * frcp(pu_);
-                    rthi[ks][e] = tf32(xr); rtlo[ks][e] = tf32r(xr - __uint_as_float(rthi[ks][e]));
-                    kthi[ks][e] = tf32(xk); ktlo[ks][e] = tf32r(xk - __uint_as_float(kthi[ks][e]));
+                for (int uh = 0; uh < 2; ++uh) {      // fragment slots e = 2*uh (row g) and 2*uh+1 (row g+8) = real channels 2g, 2g+1
+                    const int u = ks * 8 + 2 * t + uh, jr = row0 + 2 * g;
+                    const float2 pu2 = *reinterpret_cast<const float2*>(Pt + u * PK + jr);
+                    const float2 r2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(R + u * RP + jr));
+                    const float2 k2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(K + u * RP + jr));
+                    const float xr[2] = {r2.x * pp2.x, r2.y * pp2.y}, xk[2] = {k2.x * frcp(pu2.x), k2.y * frcp(pu2.y)};
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int e = 2 * uh + h;
+                        rthi[ks][e] = tf32(xr[h]); rtlo[ks][e] = tf32r(xr[h] - __uint_as_float(rthi[ks][e]));
+                        kthi[ks][e] = tf32(xk[h]); ktlo[ks][e] = tf32r(xk[h] - __uint_as_float(kthi[ks][e]));
+                    }
+                    pp2 = pu2;
                 }
+            }
             gemm_rs2<2, 2>(Z1, rthi, rtlo, Gn, PU, g, t);     // (B[k=t][n=s] = G[s][t])
             gemm_rs2<2, 2>(Z2, kthi, ktlo, Gt, PU, g, t);     // (B[k=s][n=t] = G[s][t])
         }
@@ -494,9 +508,10 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = row0 + g + ((e & 2) ? 8 : 0), i = nt * 8 + 2 * t + (e & 1);
-                A0[e >> 1] = fmaf(ET[nt][e], S0[i * PS0 + j], A0[e >> 1]);
+            for (int q = 0; q < 2; ++q) {         // ET rows (g, g+8) = real key channels (2g, 2g+1)
+                const float2 sv = *reinterpret_cast<const float2*>(S0 + (nt * 8 + 2 * t + q) * PS0 + row0 + 2 * g);
+                A0[0] = fmaf(ET[nt][q], sv.x, A0[0]);
+                A0[1] = fmaf(ET[nt][2 + q], sv.y, A0[1]);
             }
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
@@ -511,23 +526,37 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1, j = row0 + g + h * 8, tt = nt * 8 + 2 * t + (e & 1);
-                const float p = Pt[tt * PK + j];
-                const float pp = tt > 0 ? Pt[(tt - 1) * PK + j] : 1.f;
-                const float dks = Z1[nt][e] * frcp(p), drs = Z2[nt][e] * pp;
-                const float rr = to_f(R[tt * RP + j]), kk = to_f(K[tt * RP + j]);
-                const float gu_ = Gam[tt] * (h ? u1 : u0);
-                const i64 o = tok0 + (i64)(c * L + tt) * C + j;
-                gk_[o] = __float2bfloat16_rn(fmaf(gu_, rr, dks));
-                gr_[o] = __float2bfloat16_rn(fmaf(gu_, kk, drs));
-                gu_acc[h] = fmaf(Gam[tt], rr * kk, gu_acc[h]);
-                rdr[nt][e] = rr * drs;
-                cterm[nt][e] = rdr[nt][e] - kk * dks;
-                lw[nt][e] = Lg[tt * PK + j];
+            for (int q = 0; q < 2; ++q) {         // token tt, both rows of the thread: real channels jr, jr+1
+                const int tt = nt * 8 + 2 * t + q, jr = row0 + 2 * g;
+                const float2 p2 = *reinterpret_cast<const float2*>(Pt + tt * PK + jr);
+                float2 pp2 = make_float2(1.f, 1.f);
+                if (tt > 0) pp2 = *reinterpret_cast<const float2*>(Pt + (tt - 1) * PK + jr);
+                const float2 lg2 = *reinterpret_cast<const float2*>(Lg + tt * PK + jr);
+                const float2 r2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(R + tt * RP + jr));
+                const float2 k2 = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(K + tt * RP + jr));
+                const float pv[2] = {p2.x, p2.y}, ppv[2] = {pp2.x, pp2.y}, lgv[2] = {lg2.x, lg2.y};
+                const float rv[2] = {r2.x, r2.y}, kv[2] = {k2.x, k2.y}, uv[2] = {u0, u1};
+                const float gam = Gam[tt];
+                float dk[2], dr[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int e = 2 * h + q;
+                    const float dks = Z1[nt][e] * frcp(pv[h]), drs = Z2[nt][e] * ppv[h];
+                    const float gu_ = gam * uv[h];
+                    dk[h] = fmaf(gu_, rv[h], dks);
+                    dr[h] = fmaf(gu_, kv[h], drs);
+                    gu_acc[h] = fmaf(gam, rv[h] * kv[h], gu_acc[h]);
+                    rdr[nt][e] = rv[h] * drs;
+                    cterm[nt][e] = rdr[nt][e] - kv[h] * dks;
+                    lw[nt][e] = lgv[h];
+                }
+                const i64 o = tok0 + (i64)(c * L + tt) * C + jr;
+                *reinterpret_cast<uint32_t*>(gk_ + o) = f2_to_bf16x2(dk[0], dk[1]);
+                *reinterpret_cast<uint32_t*>(gr_ + o) = f2_to_bf16x2(dr[0], dr[1]);
             }
         // exclusive prefix of cterm along the 16 tokens of each row: lanes t = 0..3 of a quad hold
         // tokens (2t, 2t+1) of tile 0 and (8+2t, 8+2t+1) of tile 1
+        float Gw[2][4];
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
             const int e0 = h2 * 2;
@@ -539,14 +568,21 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             if (t >= 2) { i0 += n0; i1 += n1; }
             const float tot0 = __shfl_sync(0xffffffffu, i0, 3, 4);
             const float ex0 = i0 - p0, ex1 = tot0 + i1 - p1;
-            const int j = row0 + g + h2 * 8;
             const float pre[4] = {ex0, ex0 + cterm[0][e0], ex1, ex1 + cterm[1][e0]};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const int nt = q >> 1, e = e0 + (q & 1), tt = nt * 8 + 2 * t + (q & 1);
-                const float Gd = A0[h2] - pre[q] - rdr[nt][e];
-                if (gw_reduce) gw_acc[h2] = fmaf(Gd, lw[nt][e], gw_acc[h2]);
-                else gw_[tok0 + (i64)(c * L + tt) * C + j] = __float2bfloat16_rn(Gd * lw[nt][e]);
+                const int nt = q >> 1, e = e0 + (q & 1);
+                Gw[h2][q] = (A0[h2] - pre[q] - rdr[nt][e]) * lw[nt][e];
+            }
+        }
+        if (gw_reduce) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { gw_acc[0] += Gw[0][q]; gw_acc[1] += Gw[1][q]; }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int tt = (q >> 1) * 8 + 2 * t + (q & 1);
+                *reinterpret_cast<uint32_t*>(gw_ + tok0 + (i64)(c * L + tt) * C + row0 + 2 * g) = f2_to_bf16x2(Gw[0][q], Gw[1][q]);
             }
         }
     }
@@ -556,11 +592,11 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     for (int h2 = 0; h2 < 2; ++h2) {
         gu_acc[h2] += __shfl_xor_sync(0xffffffffu, gu_acc[h2], 1);
         gu_acc[h2] += __shfl_xor_sync(0xffffffffu, gu_acc[h2], 2);
-        if (t == 0) gu_[(i64)bb * C + hh * N + row0 + g + h2 * 8] = __float2bfloat16_rn(gu_acc[h2]);
+        if (t == 0) gu_[(i64)bb * C + hh * N + row0 + 2 * g + h2] = __float2bfloat16_rn(gu_acc[h2]);
         if (gw_reduce) {
             gw_acc[h2] += __shfl_xor_sync(0xffffffffu, gw_acc[h2], 1);
             gw_acc[h2] += __shfl_xor_sync(0xffffffffu, gw_acc[h2], 2);
-            if (t == 0) gw_[(i64)bb * C + hh * N + row0 + g + h2 * 8] = __float2bfloat16_rn(gw_acc[h2]);
+            if (t == 0) gw_[(i64)bb * C + hh * N + row0 + 2 * g + h2] = __float2bfloat16_rn(gw_acc[h2]);
         }
     }
     if (ds0_kind != 0) {
@@ -568,7 +604,7 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-                store_ds0(ds0_, ds0_kind, sbase + (row0 + g + ((e & 2) ? 8 : 0)) * N + nt * 8 + 2 * t + (e & 1), E[nt][e]);
+                store_ds0(ds0_, ds0_kind, sbase + (row0 + g + ((e & 2) ? 8 : 0)) * N + key_real(nt * 8 + 2 * t + (e & 1)), E[nt][e]);
     }
 }
 
