@@ -7,10 +7,12 @@
 // gradients: operand preparation, the four U matrices and the 16x16 inverse.  Here a second group
 // of four warps (the producers) does exactly that work one chunk ahead, into a second set of operand
 // arrays, while the first four warps (the consumers, who own E and ET) run the rest of the chunk.
+// The producers also take the consumers' last step off their hands: the per-token epilogue (dr, dw,
+// dk, da, db from Z1, Z2 and A0, handed over through shared memory), one chunk behind.
 // One CTA-wide barrier per chunk hands the finished set over and returns the other; inside a group
 // the barriers are named barriers of 128 threads.  Input tiles go through a ring of three stages
 // (read by the consumers' epilogue, read by the producers, in flight).  Same arithmetic, same
-// fragment layouts and results as wkv7_chunked_bwd.cu; 164 KB of shared memory, one CTA per SM.
+// fragment layouts and results as wkv7_chunked_bwd.cu; 201 KB of shared memory, one CTA per SM.
 #include "wkv7_chunked.cuh"
 #include "wkv7_dispatch.cuh"
 
@@ -31,7 +33,8 @@ struct SSmem {
     static constexpr int kEv = kS0 + N * PS0;                        // EV [t][i]
     static constexpr int kP = kEv + L * PK;                          // P1..P4 natural, then transposed
     static constexpr int kHalf = kP + 8 * L * PU;
-    static constexpr int kEnd = kHalf + 2 * N;
+    static constexpr int kZb = kHalf + 2 * N;                        // [2][9][NT] float4: Z1, Z2 and A0 of a finished chunk
+    static constexpr int kEnd = kZb + 2 * 9 * NT * 4;
     static constexpr int kBytes = kEnd * 4;
 };
 static_assert(SSmem::kBytes <= 227 * 1024, "shared memory of the producer/consumer backward");
@@ -189,6 +192,90 @@ wkv7s_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
     };
 
+    // per-token gradients of a finished chunk ce from its Z1 (dK', dB'), Z2 (dA', dR') and A0: rows = real
+    // key channels row0+2g (+1), columns = tokens.  Run by the producers, one chunk behind the consumers.
+    auto epilogue = [&](int ce) {
+        const int stage = ce % 3;
+        const float* Wt = sm + SSmem::kSets + (ce & 1) * kSetFloats + 6 * L * PK;
+        const bf16* R = raw + (stage * 7 + 0) * L * RP;
+        const bf16* Wr = raw + (stage * 7 + 1) * L * RP;
+        const bf16* K = raw + (stage * 7 + 2) * L * RP;
+        const bf16* A = raw + (stage * 7 + 4) * L * RP;
+        const bf16* Bv = raw + (stage * 7 + 5) * L * RP;
+        float Z1[4][4], Z2[4][4], A0[2];
+        {
+            const float4* zb = reinterpret_cast<const float4*>(sm + SSmem::kZb) + (ce & 1) * 9 * NT + tid;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 x = zb[q * NT], y = zb[(4 + q) * NT];
+                Z1[q][0] = x.x; Z1[q][1] = x.y; Z1[q][2] = x.z; Z1[q][3] = x.w;
+                Z2[q][0] = y.x; Z2[q][1] = y.y; Z2[q][2] = y.z; Z2[q][3] = y.w;
+            }
+            const float4 a0 = zb[8 * NT];
+            A0[0] = a0.x; A0[1] = a0.y;
+        }
+        float cterm[2][4], ada[2][4], sgd[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {         // token tt, both rows of the thread: real channels jr, jr+1
+                const int tt = nt * 8 + 2 * t + q, jr = row0 + 2 * g;
+                const float2 wt = *reinterpret_cast<const float2*>(Wt + tt * PK + jr);
+                float2 wprev = make_float2(1.f, 1.f);
+                if (tt > 0) wprev = *reinterpret_cast<const float2*>(Wt + (tt - 1) * PK + jr);
+                const float2 rr = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(R + tt * RP + jr));
+                const float2 aa = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(A + tt * RP + jr));
+                const float2 bq = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Bv + tt * RP + jr));
+                const float2 kq = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(K + tt * RP + jr));
+                const float2 wr = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Wr + tt * RP + jr));
+                const float wtv[2] = {wt.x, wt.y}, wpv[2] = {wprev.x, wprev.y};
+                const float rv[2] = {rr.x, rr.y}, av[2] = {aa.x, aa.y}, bv2[2] = {bq.x, bq.y}, kv[2] = {kq.x, kq.y}, wv[2] = {wr.x, wr.y};
+                float dk[2], db[2], da[2], dr[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int e = 2 * h + q;
+                    const float iw = frcp(wtv[h]);
+                    dk[h] = Z1[nt][e] * iw; db[h] = Z1[2 + nt][e] * iw;
+                    da[h] = Z2[nt][e] * wpv[h]; dr[h] = Z2[2 + nt][e] * wtv[h];
+                    ada[nt][e] = av[h] * da[h];
+                    cterm[nt][e] = rv[h] * dr[h] + ada[nt][e] - bv2[h] * db[h] - kv[h] * dk[h];
+                    const float sg = frcp(1.f + fexp(-wv[h]));
+                    sgd[nt][e] = kWScale * sg * (1.f - sg);
+                }
+                const i64 o = tok0 + (i64)(ce * L + tt) * C + jr;
+                *reinterpret_cast<uint32_t*>(dk_ + o) = f2_to_bf16x2(dk[0], dk[1]);
+                *reinterpret_cast<uint32_t*>(db_ + o) = f2_to_bf16x2(db[0], db[1]);
+                *reinterpret_cast<uint32_t*>(da_ + o) = f2_to_bf16x2(da[0], da[1]);
+                *reinterpret_cast<uint32_t*>(dr_ + o) = f2_to_bf16x2(dr[0], dr[1]);
+            }
+        // exclusive prefix of cterm along the 16 tokens of each row: lanes t = 0..3 of a quad hold
+        // tokens (2t, 2t+1) of tile 0 and (8+2t, 8+2t+1) of tile 1
+        float G[2][4];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const int e0 = h2 * 2;
+            const float p0 = cterm[0][e0] + cterm[0][e0 + 1], p1 = cterm[1][e0] + cterm[1][e0 + 1];
+            float i0 = p0, i1 = p1;                          // inclusive scans over the quad
+            float n0 = __shfl_up_sync(0xffffffffu, i0, 1, 4), n1 = __shfl_up_sync(0xffffffffu, i1, 1, 4);
+            if (t >= 1) { i0 += n0; i1 += n1; }
+            n0 = __shfl_up_sync(0xffffffffu, i0, 2, 4); n1 = __shfl_up_sync(0xffffffffu, i1, 2, 4);
+            if (t >= 2) { i0 += n0; i1 += n1; }
+            const float tot0 = __shfl_sync(0xffffffffu, i0, 3, 4);
+            const float ex0 = i0 - p0, ex1 = tot0 + i1 - p1;
+            const float pre[4] = {ex0, ex0 + cterm[0][e0], ex1, ex1 + cterm[1][e0]};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int nt = q >> 1, e = e0 + (q & 1);
+                G[h2][q] = (A0[h2] - pre[q] - ada[nt][e]) * sgd[nt][e];
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int tt = (q >> 1) * 8 + 2 * t + (q & 1);
+            *reinterpret_cast<uint32_t*>(dw_ + tok0 + (i64)(ce * L + tt) * C + row0 + 2 * g) = f2_to_bf16x2(G[0][q], G[1][q]);
+        }
+    };
+
     if (producer) {
         issue_raw(nchunks - 1);
         if (nchunks > 1) issue_raw(nchunks - 2); else cp_async_commit();
@@ -202,8 +289,12 @@ wkv7s_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
     for (int c = nchunks - 1; c >= 0; --c) {
         if (producer) {
+            if (c + 1 < nchunks) {
+                epilogue(c + 1);   // needs the tiles and W_t of chunk c+1, which the steps below overwrite
+                group_sync();
+            }
             if (c > 0) {
-                if (c > 1) issue_raw(c - 2); else cp_async_commit();   // its stage held chunk c+1, which the consumers have left
+                if (c > 1) issue_raw(c - 2); else cp_async_commit();   // its stage held chunk c+1, which nobody reads any more
                 cp_async_wait<1>();                                      // the tiles of chunk c-1 have landed
                 group_sync();
                 produce(c - 1);
@@ -216,7 +307,6 @@ wkv7s_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             float *Uab = Wt + L * PK, *Uak = Uab + L * PU, *Ubr = Uak + L * PU, *Ukr = Ubr + L * PU, *Tn = Ukr + L * PU;
             float* We = Uab + 5 * L * PU;
             const bf16* R = raw + (stage * 7 + 0) * L * RP;
-            const bf16* Wr = raw + (stage * 7 + 1) * L * RP;
             const bf16* K = raw + (stage * 7 + 2) * L * RP;
             const bf16* A = raw + (stage * 7 + 4) * L * RP;
             const bf16* Bv = raw + (stage * 7 + 5) * L * RP;
@@ -385,70 +475,20 @@ wkv7s_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
             group_sync();      // every warp is done with sa and the staged state
             if (c > 0) issue_state(c - 1);
-            float cterm[2][4], ada[2][4], sgd[2][4];
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {         // token tt, both rows of the thread: real channels jr, jr+1
-                    const int tt = nt * 8 + 2 * t + q, jr = row0 + 2 * g;
-                    const float2 wt = *reinterpret_cast<const float2*>(Wt + tt * PK + jr);
-                    float2 wprev = make_float2(1.f, 1.f);
-                    if (tt > 0) wprev = *reinterpret_cast<const float2*>(Wt + (tt - 1) * PK + jr);
-                    const float2 rr = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(R + tt * RP + jr));
-                    const float2 aa = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(A + tt * RP + jr));
-                    const float2 bq = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Bv + tt * RP + jr));
-                    const float2 kq = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(K + tt * RP + jr));
-                    const float2 wr = bf16x2_to_f2(*reinterpret_cast<const uint32_t*>(Wr + tt * RP + jr));
-                    const float wtv[2] = {wt.x, wt.y}, wpv[2] = {wprev.x, wprev.y};
-                    const float rv[2] = {rr.x, rr.y}, av[2] = {aa.x, aa.y}, bv2[2] = {bq.x, bq.y}, kv[2] = {kq.x, kq.y}, wv[2] = {wr.x, wr.y};
-                    float dk[2], db[2], da[2], dr[2];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int e = 2 * h + q;
-                        const float iw = frcp(wtv[h]);
-                        dk[h] = Z1[nt][e] * iw; db[h] = Z1[2 + nt][e] * iw;
-                        da[h] = Z2[nt][e] * wpv[h]; dr[h] = Z2[2 + nt][e] * wtv[h];
-                        ada[nt][e] = av[h] * da[h];
-                        cterm[nt][e] = rv[h] * dr[h] + ada[nt][e] - bv2[h] * db[h] - kv[h] * dk[h];
-                        const float sg = frcp(1.f + fexp(-wv[h]));
-                        sgd[nt][e] = kWScale * sg * (1.f - sg);
-                    }
-                    const i64 o = tok0 + (i64)(c * L + tt) * C + jr;
-                    *reinterpret_cast<uint32_t*>(dk_ + o) = f2_to_bf16x2(dk[0], dk[1]);
-                    *reinterpret_cast<uint32_t*>(db_ + o) = f2_to_bf16x2(db[0], db[1]);
-                    *reinterpret_cast<uint32_t*>(da_ + o) = f2_to_bf16x2(da[0], da[1]);
-                    *reinterpret_cast<uint32_t*>(dr_ + o) = f2_to_bf16x2(dr[0], dr[1]);
-                }
-            // exclusive prefix of cterm along the 16 tokens of each row: lanes t = 0..3 of a quad hold
-            // tokens (2t, 2t+1) of tile 0 and (8+2t, 8+2t+1) of tile 1
-            float G[2][4];
-#pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-                const int e0 = h2 * 2;
-                const float p0 = cterm[0][e0] + cterm[0][e0 + 1], p1 = cterm[1][e0] + cterm[1][e0 + 1];
-                float i0 = p0, i1 = p1;                          // inclusive scans over the quad
-                float n0 = __shfl_up_sync(0xffffffffu, i0, 1, 4), n1 = __shfl_up_sync(0xffffffffu, i1, 1, 4);
-                if (t >= 1) { i0 += n0; i1 += n1; }
-                n0 = __shfl_up_sync(0xffffffffu, i0, 2, 4); n1 = __shfl_up_sync(0xffffffffu, i1, 2, 4);
-                if (t >= 2) { i0 += n0; i1 += n1; }
-                const float tot0 = __shfl_sync(0xffffffffu, i0, 3, 4);
-                const float ex0 = i0 - p0, ex1 = tot0 + i1 - p1;
-                const float pre[4] = {ex0, ex0 + cterm[0][e0], ex1, ex1 + cterm[1][e0]};
+            {   // Z1, Z2 and A0 go to the producers, who turn them into dr, dw, dk, da, db while the next chunk runs
+                float4* zb = reinterpret_cast<float4*>(sm + SSmem::kZb) + (c & 1) * 9 * NT + tid;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const int nt = q >> 1, e = e0 + (q & 1);
-                    G[h2][q] = (A0[h2] - pre[q] - ada[nt][e]) * sgd[nt][e];
+                    zb[q * NT] = make_float4(Z1[q][0], Z1[q][1], Z1[q][2], Z1[q][3]);
+                    zb[(4 + q) * NT] = make_float4(Z2[q][0], Z2[q][1], Z2[q][2], Z2[q][3]);
                 }
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int tt = (q >> 1) * 8 + 2 * t + (q & 1);
-                *reinterpret_cast<uint32_t*>(dw_ + tok0 + (i64)(c * L + tt) * C + row0 + 2 * g) = f2_to_bf16x2(G[0][q], G[1][q]);
+                zb[8 * NT] = make_float4(A0[0], A0[1], 0.f, 0.f);
             }
         }
         __syncthreads();   // hand-over: the set of chunk c-1 is complete, the set and the tiles of chunk c are free
     }
 
+    if (producer) epilogue(0);
     if (!producer && ds0_ != nullptr) {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {   // logical columns of tiles 2m, 2m+1 = real columns 16m + 4t .. 16m + 4t + 3
