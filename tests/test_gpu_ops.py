@@ -141,7 +141,7 @@ def test_wkv5_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,H,N", [(2, 96, 2, 64), (2, 256, 3, 64), (1, 40, 2, 128), (2, 33, 3, 17), (3, 5, 2, 4), (2, 70, 1, 32)])
+@pytest.mark.parametrize("B,T,H,N", [(2, 96, 2, 64), (2, 256, 3, 64), (1, 16, 1, 64), (1, 40, 2, 128), (2, 33, 3, 17), (3, 5, 2, 4), (2, 70, 1, 32)])
 def test_wkv5_oracle(R, dtype, B, T, H, N):
     g = Hh.gen(42)
     C = H * N
@@ -235,7 +235,7 @@ def test_wkv6_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,H,N", [(2, 300, 2, 64), (2, 256, 2, 64), (2, 7, 2, 4), (1, 50, 1, 128), (2, 41, 3, 17)])
+@pytest.mark.parametrize("B,T,H,N", [(2, 300, 2, 64), (2, 256, 2, 64), (1, 16, 1, 64), (2, 32, 3, 64), (2, 7, 2, 4), (1, 50, 1, 128), (2, 41, 3, 17)])
 def test_wkv6_oracle(R, dtype, B, T, H, N):
     """T = 300 is beyond what the reference backward can run (wkv6/run.py:51)."""
     g = Hh.gen(42)
@@ -272,7 +272,7 @@ def test_wkv6state_golden(R, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,H,N", [(2, 200, 2, 64), (2, 192, 2, 64), (3, 7, 2, 4)])
+@pytest.mark.parametrize("B,T,H,N", [(2, 200, 2, 64), (2, 192, 2, 64), (1, 16, 2, 64), (3, 7, 2, 4)])
 def test_wkv6state_oracle(R, dtype, B, T, H, N):
     g = Hh.gen(42)
     C = H * N
@@ -414,3 +414,32 @@ def test_wkv7_state_passing_composes(R):
     yb, sT2 = fwd(48, T, sm)
     assert torch.equal(torch.cat([ya, yb], 1), y)
     assert torch.equal(sT2, sT)
+
+
+def test_wkv6_chunked_calls_on_two_streams(R):
+    """Two chunked RWKV-6 calls in flight on different streams, one of them with decays that force
+    the fall-back: each call has its own device flag, so neither disturbs the other."""
+    B, T, H, N = 2, 128, 2, 64
+    dtype = torch.bfloat16
+    C = H * N
+    results = {}
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    cases = {}
+    for idx, shift in enumerate((-3.0, 5.0)):
+        g = Hh.gen(20 + idx)
+        r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+        w_raw, u = Hh.randn(g, B, T, C) + shift, Hh.rand(g, H, N, lo=-1, hi=1)
+        xs = [x.to(dtype).double() for x in (r, k, v, w_raw, u)]
+        cases[idx] = (O.wkv6(*xs, H), [x.to(dtype).to(DEV).contiguous() for x in (r, k, v)],
+                      (-torch.exp(w_raw.to(dtype).float())).to(DEV).contiguous(), u.to(dtype).to(DEV).contiguous())
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for idx, st in enumerate(streams):
+            _, (rd, kd, vd), ew, ud = cases[idx]
+            with torch.cuda.stream(st):
+                y = sentinel(B, T, C, dtype=dtype)
+                R.ops.wkv6_forward(B, T, C, H, rd, kd, vd, ew, ud, y)
+                results[idx] = y
+    torch.cuda.synchronize()
+    for idx in cases:
+        Hh.assert_close(results[idx], cases[idx][0], Hh.tol_for(dtype), f"wkv6 stream {idx}")
