@@ -202,8 +202,9 @@ int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len,
                            void* da, void* db, void* stream);
 
 /* Kernel choice for RWKV-7 (process-wide; set it before launching work, not concurrently with it):
- * 0 = automatic (for bf16, N=64, chunk_len=16: setting 3, or 5 when B*H does not exceed the number
- *     of SMs; general-shape kernels otherwise),
+ * 0 = automatic (for bf16, N=64, chunk_len=16: setting 3, with the kernels of setting 5 for small
+ *     launches (forward: B*H up to twice the number of SMs, backward: up to the number of SMs);
+ *     general-shape kernels otherwise),
  * 1 = general-shape kernels only, 2 = mma.sync tensor-core kernels, 3 = tcgen05 forward with the
  * mma.sync backward, 4 = tcgen05 forward and backward, 5 = the producer/consumer forms of the
  * tcgen05 forward and the mma.sync backward (2 to 5 refuse other shapes).

@@ -46,8 +46,8 @@ extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 
 // 0 = automatic (= 3 where applicable), 1 = general-shape kernels only, 2 = mma.sync chunked kernels,
 // 3 = tcgen05 forward + chunked backward, 4 = tcgen05 forward and backward,
-// 5 = producer/consumer forms of the tcgen05 forward and the chunked backward.  Automatic takes 5
-// instead of 3 when the launch puts at most one (batch, head) unit on an SM.
+// 5 = producer/consumer forms of the tcgen05 forward and the chunked backward.  Automatic takes them
+// instead of 3 for small launches: the forward up to two (batch, head) units per SM, the backward up to one.
 static int g_wkv7_path = 0;
 
 static int sm_count() {
@@ -109,9 +109,10 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
     if (chunked) {
         RWKV_REQUIRE(aligned16({s0, r, w, k, v, a, b, y, sT, s, sa}), RWKVB200_EALIGN,
                      "wkv7_forward: the bf16 N=64 path needs 16-byte aligned tensors");
-        // one unit per SM or fewer: the time is one unit's chain of chunks, which the producer/consumer
-        // kernel shortens; with more units per SM four plain CTAs per SM give more throughput
-        if (g_wkv7_path == 5 || (g_wkv7_path == 0 && (long long)B * H <= sm_count()))
+        // up to two units per SM: the time is (close to) one unit's chain of chunks, which the
+        // producer/consumer kernel shortens (it fits two CTAs per SM); with more units per SM four plain
+        // CTAs per SM give more throughput (B=4 at H=64: 0.72 vs 0.78 ms; B=8: 1.41 vs 1.34 ms)
+        if (g_wkv7_path == 5 || (g_wkv7_path == 0 && (long long)B * H <= 2LL * sm_count()))
             return wkv7_umma_split_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
         if (g_wkv7_path != 2)   // automatic, 3 and 4: the tcgen05 forward
             return wkv7_umma_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));

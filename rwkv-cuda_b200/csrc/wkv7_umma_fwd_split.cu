@@ -1,6 +1,6 @@
 // RWKV-7 forward, head size 64, bf16 activations: the tcgen05 kernel of wkv7_umma_fwd.cu as a
-// producer/consumer pair, for launches that put at most one (batch, head) unit on an SM
-// (B*H <= number of SMs: strong scaling over GPUs at a small batch per GPU).
+// producer/consumer pair, for launches that put at most two (batch, head) units on an SM
+// (strong scaling over GPUs at a small batch per GPU).  110 registers, 86 KB: two CTAs fit an SM.
 //
 // With one CTA per SM the time of the forward is the length of one unit's chain of chunks, and half
 // of every chunk in wkv7_umma_fwd.cu does not depend on the state: operand preparation, the U
@@ -46,7 +46,7 @@ struct Smem {
 static_assert(SetMap::kBytes % 128 == 0, "operand sets keep the 128-byte alignment of their first array");
 static_assert(2 * L * PS * 4 <= 2 * 16 * LBO_T, "y/sa staging reuses the token-major operand arrays");
 
-__global__ void __launch_bounds__(NTS, 1)
+__global__ void __launch_bounds__(NTS, 2)
 wkv7us_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __restrict__ r_,
                       const bf16* __restrict__ w_, const bf16* __restrict__ k_, const bf16* __restrict__ v_,
                       const bf16* __restrict__ a_, const bf16* __restrict__ b_, bf16* __restrict__ y_,

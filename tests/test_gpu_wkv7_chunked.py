@@ -83,7 +83,7 @@ def _set_path(p):
     _lib.call("rwkvb200_wkv7_select_path", p)
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 64, 3), (3, 32, 64)])
+@pytest.mark.parametrize("B,T,H", [(1, 64, 3), (3, 32, 64), (5, 32, 64)])
 def test_kernel_choice_by_grid_size_is_bit_exact(B, T, H):
     """The producer/consumer kernels (small grids) and the plain ones (B*H above the SM count) do the
     same arithmetic in the same order: forced either way, and chosen automatically on both sides of
