@@ -58,7 +58,7 @@ static int sm_count() {
 }
 
 extern "C" int rwkvb200_wkv7_select_path(int path) {
-    RWKV_REQUIRE(path >= 0 && path <= 5, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..5", path);
+    RWKV_REQUIRE(path >= 0 && path <= 6, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..6", path);
     g_wkv7_path = path;
     return RWKVB200_OK;
 }
@@ -92,6 +92,8 @@ static int wkv7_check(const char* what, int dtype, int B, int T, int H, int N, i
 
 extern "C" int rwkvb200_device_status(void) {
     if (const int f = wkv7_umma_error()) return f;
+    if (const int f = wkv7_l32_fwd_error()) return 10 + f;
+    if (const int f = wkv7_l32_bwd_error()) return 20 + f;
     if (const int f = wkv7_umma_split_error()) return f;
     return wkv7_umma_bwd_error();
 }
@@ -112,6 +114,8 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
         // up to two units per SM: the time is (close to) one unit's chain of chunks, which the
         // producer/consumer kernel shortens (it fits two CTAs per SM); with more units per SM four plain
         // CTAs per SM give more throughput (B=4 at H=64: 0.72 vs 0.78 ms; B=8: 1.41 vs 1.34 ms)
+        if (g_wkv7_path == 6)
+            return wkv7_l32_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
         if (g_wkv7_path == 5 || (g_wkv7_path == 0 && (long long)B * H <= 2LL * sm_count()))
             return wkv7_umma_split_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
         if (g_wkv7_path != 2)   // automatic, 3 and 4: the tcgen05 forward
@@ -134,6 +138,8 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
     if (chunked) {
         RWKV_REQUIRE(aligned16({r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db}), RWKVB200_EALIGN,
                      "wkv7_backward: the bf16 N=64 path needs 16-byte aligned tensors");
+        if (g_wkv7_path == 6)
+            return wkv7_l32_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, ds0, dr, dw, dk, dv, da, db, as_stream(stream));
         if (g_wkv7_path == 4)
             return wkv7_umma_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
                                       as_stream(stream));

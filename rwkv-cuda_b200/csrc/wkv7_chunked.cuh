@@ -236,7 +236,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // g_phase_clocks[warp][phase].  Each translation unit that uses the marks has its own copy and
 // exports a reader next to its kernel.
 #ifdef RWKVB200_PHASE_CLOCKS
-static __device__ unsigned long long g_phase_clocks[4][16];
+static __device__ unsigned long long g_phase_clocks[8][16];
 #define WKV7_PHASE_BEGIN() long long phase_last_ = clock64()
 #define WKV7_PHASE(k)                                                                              \
     do {                                                                                           \

@@ -43,4 +43,14 @@ int wkv7_chunked_backward(int B, int T, int H, const void* r, const void* w, con
                           const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv, void* da, void* db,
                           cudaStream_t st);
 
+// 32-token chunks, every product on tcgen05 with the dependent products chained through tensor memory.
+// Saved buffer: chunk-start states every 32 tokens in `s` (first half), `sa` unused.
+int wkv7_l32_forward(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k, const void* v,
+                     const void* a, const void* b, void* y, float* sT, float* s, float* sa, cudaStream_t st);
+int wkv7_l32_fwd_error();
+int wkv7_l32_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v, const void* a,
+                      const void* b, const void* dy, const float* dsT, const float* s, float* ds0, void* dr, void* dw,
+                      void* dk, void* dv, void* da, void* db, cudaStream_t st);
+int wkv7_l32_bwd_error();
+
 }  // namespace rwkvb200
