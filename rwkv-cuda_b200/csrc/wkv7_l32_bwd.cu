@@ -47,7 +47,7 @@ struct BwdSmemX {
     static constexpr int kWe = kLam + 32 * 64 * 4;       // [64]
     static constexpr int kA0 = kWe + 256;                // [2][64] partial anchors
     static constexpr int kCarry = kA0 + 512;             // [64] sum of c over the first 16 tokens
-    static constexpr int kBar = kCarry + 256;            // 6 mbarriers + tmem slot
+    static constexpr int kBar = kCarry + 256;            // 7 mbarriers + tmem slot
     static constexpr int kBytes = kBar + 64 + 1024;      // + slack to start on a 1024-byte boundary
     // inside the EV rows of EY (two pieces of 4096 bytes), free until EV is written: the exchange buffer
     // and the two diagonal blocks of U_ab, plain fp32 [2][16][BPITCH]
@@ -106,7 +106,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     float* Hs = reinterpret_cast<float*>(smem + BwdSmemX::kHs);
     float* Uab = reinterpret_cast<float*>(smem + BwdSmemX::kUab);
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + BwdSmemX::kBar);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 6);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 7);
 
     const int hh = blockIdx.x, bb = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -122,7 +122,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 6; ++i) mbar_init(bar + i);
+        for (int i = 0; i < 7; ++i) mbar_init(bar + i);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -169,7 +169,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     fetch_chunk<7, BTPW>(raw, src, tok0, C, nchunks - 1, T, warp, lane);
     int fail = 0;
     uint32_t par = 0;
-    ChainSync cs{bar + 5, 0, 0};   // used by warp 0 only
+    ChainSync cs{bar + 6, 0, 0};   // used by warp 0 only
 
     WKV7_PHASE_BEGIN();
     for (int c = nchunks - 1; c >= 0; --c, par ^= 1) {
@@ -188,16 +188,19 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         // ---- 1. operands ---------------------------------------------------------------------------
         prepare_operands<7, BTPW, 8>(raw, valid, AR, BK, SV + 32 * 128, HALF64, EY + 32 * 128, HALF64, We, Hs, Lam, warp, lane);
         WKV7_PHASE(1);   // operand preparation
+        cp_async_wait<0>();   // the chunk-start state
         proxy_fence();
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
-        if (c > 0) fetch_chunk<7, BTPW>(raw, src, tok0, C, c - 1, T, warp, lane);
-        WKV7_PHASE(2);   // barrier, fetch issue
+        WKV7_PHASE(2);   // barrier
         // ---- 2. U ------------------------------------------------------------------------------------
         if (warp == 0) {
             issue_u(tmW1, arA, bkA, lead);
             mma_commit(bar, lead);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)   // X_a = S0 A~^T, needed after the inverse only
+                mma_ss(tmW2, desc_k(s0A, 0, ks * 8, HALF64), desc_k(arA, 0, ks * 8, HALF64), idesc64(32, 0, 0), ks > 0, lead);
         }
         if (!mbar_wait(bar, par)) fail = 1;
         tc_fence_after();
@@ -212,7 +215,6 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         tc_fence_before();
         __syncthreads();
         if (warp < 2) tri_inverse16<BPITCH>(Uab + warp * 16 * BPITCH, D0, 16 * warp, lane);
-        cp_async_wait<0>();
         proxy_fence();
         tc_fence_before();
         __syncthreads();
@@ -220,9 +222,6 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         WKV7_PHASE(4);   // masked U, inverse
         // ---- 4. the forward part again: SA ----------------------------------------------------------------
         if (warp == 0) {
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)   // X_a = S0 A~^T
-                mma_ss(tmW2, desc_k(s0A, 0, ks * 8, HALF64), desc_k(arA, 0, ks * 8, HALF64), idesc64(32, 0, 0), ks > 0, lead);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)   // Z = X_a + V U_ak
                 mma_ss(tmW2, desc_mn(svA + 32 * 128, ks * 8, HALF64), desc_mn(uakA, ks * 8, HALF32), idesc64(32, 1, 1), 1, lead);
@@ -247,7 +246,8 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tmem_st_tiles<4>(tmET + 32 * hs + lane_off, Td);
             tmem_wait_st();
         }
-        WKV7_PHASE(5);   // issue of the forward part, decay scaling of E
+        if (c > 0) fetch_chunk<7, BTPW>(raw, src, tok0, C, c - 1, T, warp, lane);   // under the chain
+        WKV7_PHASE(5);   // issue of the forward part, decay scaling of E, request of the next chunk
         if (!mbar_wait(bar + 1, par)) fail = 2;
         tc_fence_after();
         WKV7_PHASE(6);   // wait for SA
@@ -313,12 +313,23 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
         tc_fence_after();
         WKV7_PHASE(9);   // EV to shared memory, dv out
-        // ---- 6. P -----------------------------------------------------------------------------------------
+        // ---- 6. P; with it what needs EV but not P: the E^T part of [dB'|dK'] and the state gradient ------
         if (warp == 0) {
+            const uint32_t idkk = idesc64(64, 0, 0), idmm = idesc64(64, 1, 1);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
-                mma_ss(tmW2, desc_k(eyA, 0, ks * 8, HALF64), desc_k(svA, 0, ks * 8, HALF64), idesc64(64, 0, 0), ks > 0, lead);
+                mma_ss(tmW2, desc_k(eyA, 0, ks * 8, HALF64), desc_k(svA, 0, ks * 8, HALF64), idkk, ks > 0, lead);
             mma_commit(bar + 3, lead);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)   // [dB'|dK'] = ETw [SA;V]^T
+                mma_ts(tmW1, tmET + ks * 8, desc_k(svA, 0, ks * 8, HALF64), idkk, ks > 0, lead);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)   // E += [EV;dY] (stacked over tokens) [A~;R~]
+                mma_ss(tmE, desc_mn(eyA, ks * 8, HALF64), desc_mn(arA, ks * 8, HALF64), idmm, 1, lead);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)   // ET += [A~;R~]^T [EV;dY]
+                mma_ss(tmET, desc_mn(arA, ks * 8, HALF64), desc_mn(eyA, ks * 8, HALF64), idmm, 1, lead);
+            mma_commit(bar + 4, lead);
         }
         if (!mbar_wait(bar + 3, par)) fail = 4;
         tc_fence_after();
@@ -343,14 +354,11 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         __syncthreads();
         tc_fence_after();
         WKV7_PHASE(11);  // P to shared memory
-        // ---- 7. gradients of the scaled vectors, state gradient ----------------------------------------
+        // ---- 7. the parts of the gradients of the scaled vectors that need P --------------------------
         if (warp == 0) {
-            const uint32_t idkk = idesc64(64, 0, 0), idmm = idesc64(64, 1, 1), idmk = idesc64(64, 1, 0);
+            const uint32_t idmm = idesc64(64, 1, 1), idmk = idesc64(64, 1, 0);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)   // [dB'|dK'] = ETw [SA;V]^T
-                mma_ts(tmW1, tmET + ks * 8, desc_k(svA, 0, ks * 8, HALF64), idkk, ks > 0, lead);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)   //            + [A~;R~]^T P
+            for (int ks = 0; ks < 8; ++ks)   // [dB'|dK'] += [A~;R~]^T P
                 mma_ss(tmW1, desc_mn(arA, ks * 8, HALF64), desc_mn(pA, ks * 8, HALF64), idmm, 1, lead);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)   // [dA'|dR'] = S0^T [EV;dY]^T
@@ -358,20 +366,39 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)   //            + [B~;K~]^T P^T
                 mma_ss(tmW2, desc_mn(bkA, ks * 8, HALF64), desc_k(pA, 0, ks * 8, HALF64), idmk, 1, lead);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)   // E += [EV;dY] (stacked over tokens) [A~;R~]
-                mma_ss(tmE, desc_mn(eyA, ks * 8, HALF64), desc_mn(arA, ks * 8, HALF64), idmm, 1, lead);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)   // ET += [A~;R~]^T [EV;dY]
-                mma_ss(tmET, desc_mn(arA, ks * 8, HALF64), desc_mn(eyA, ks * 8, HALF64), idmm, 1, lead);
-            mma_commit(bar + 4, lead);
+            mma_commit(bar + 5, lead);
         }
+        // meanwhile the anchor: A0[j] = sum_i ET_new[j][i] S0[i][j]; this warp: value columns 32*hs .. 32*hs+31
         if (!mbar_wait(bar + 4, par)) fail = 5;
         tc_fence_after();
-        WKV7_PHASE(12);  // final products on the tensor core
+        {
+            float Td[4][4];
+            tmem_ld_tiles<4>(Td, tmET + 32 * hs + lane_off);
+            tmem_wait_ld();
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int i = 32 * hs + nt * 8 + 2 * t + e;
+                    acc0 = fmaf(Td[nt][e], *reinterpret_cast<const float*>(S0 + sw(i, row0 + g, HALF64)), acc0);
+                    acc1 = fmaf(Td[nt][2 + e], *reinterpret_cast<const float*>(S0 + sw(i, row0 + g + 8, HALF64)), acc1);
+                }
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+            if (t == 0) { A0p[hs * 64 + row0 + g] = acc0; A0p[hs * 64 + row0 + g + 8] = acc1; }
+        }
+        if (!mbar_wait(bar + 5, par)) fail = 7;
+        tc_fence_after();
+        WKV7_PHASE(12);  // final products on the tensor core, anchor
         // ---- 8. epilogue: this warp has key rows row0+g / +8 and tokens 16*hs .. 16*hs+15 ---------------
-        float pre[2][2][2];     // [row][tile][e]: sum of c over the earlier tokens of this half
-        float adA[2][2][2];     // a~ dA'
+        // Outputs go through staging rows in shared memory that is dead by now ([32 tokens][72] bf16 each:
+        // dr, da, dk in the SA/V array, db, dw in the P array) and leave as 16-byte pieces.
+        bf16* stg[5];
+#pragma unroll
+        for (int o = 0; o < 5; ++o) stg[o] = reinterpret_cast<bf16*>((o < 3 ? SV : Pm) + (o < 3 ? o : o - 3) * (32 * 72 * 2));
+        float gl[2][2][2];      // [row][tile][e]: sum of c over the earlier tokens of this half + a~ dA'
+        float fw[2][2][2];      // d log-decay / d raw decay input
         {
             float gB[2][4], gK[2][4], gA[2][4], gR[2][4];
             tmem_ld_tiles<2>(gB, tmW1 + 16 * hs + lane_off);
@@ -390,17 +417,17 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                         const int j = row0 + g + 8 * h, tt = 16 * hs + nt * 8 + 2 * t + e, x = 2 * h + e;
                         const float at = tf32_seen(AR + sw(tt, j, HALF64)), rt = tf32_seen(AR + sw(32 + tt, j, HALF64));
                         const float bt = tf32_seen(BK + sw(tt, j, HALF64)), kt = tf32_seen(BK + sw(32 + tt, j, HALF64));
-                        adA[h][nt][e] = at * gA[nt][x];
-                        ct[h][e] = rt * gR[nt][x] + adA[h][nt][e] - bt * gB[nt][x] - kt * gK[nt][x];
+                        const float ada = at * gA[nt][x];
+                        ct[h][e] = rt * gR[nt][x] + ada - bt * gB[nt][x] - kt * gK[nt][x];
+                        gl[h][nt][e] = ada;
                         const float lam = Lam[tt * 64 + j], lamp = tt > 0 ? Lam[(tt - 1) * 64 + j] : 0.f;
                         const float wt = fex2(lam), iw = fex2(-lam), wp = fex2(lamp);
-                        if (tt < valid) {
-                            const i64 o = tok0 + (i64)(c * LC + tt) * C + j;
-                            dr_[o] = __float2bfloat16_rn(gR[nt][x] * wt);
-                            da_[o] = __float2bfloat16_rn(gA[nt][x] * wp);
-                            dk_[o] = __float2bfloat16_rn(gK[nt][x] * iw);
-                            db_[o] = __float2bfloat16_rn(gB[nt][x] * iw);
-                        }
+                        const float sg = (lam - lamp) * (1.f / kWScale2);
+                        fw[h][nt][e] = kWScale * sg * (1.f - sg);
+                        stg[0][tt * 72 + j] = __float2bfloat16_rn(gR[nt][x] * wt);
+                        stg[1][tt * 72 + j] = __float2bfloat16_rn(gA[nt][x] * wp);
+                        stg[2][tt * 72 + j] = __float2bfloat16_rn(gK[nt][x] * iw);
+                        stg[3][tt * 72 + j] = __float2bfloat16_rn(gB[nt][x] * iw);
                     }
                 // exclusive prefix over the tokens of this tile (token = 2*t + e across the four lanes of a quad)
 #pragma unroll
@@ -412,29 +439,13 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     nb = __shfl_up_sync(0xffffffffu, inc, 2, 4);
                     if (t >= 2) inc += nb;
                     const float tot = __shfl_sync(0xffffffffu, inc, 3, 4);
-                    pre[h][nt][0] = run[h] + inc - pair;
-                    pre[h][nt][1] = pre[h][nt][0] + ct[h][0];
+                    const float p0 = run[h] + inc - pair;
+                    gl[h][nt][1] += p0 + ct[h][0];
+                    gl[h][nt][0] += p0;
                     run[h] += tot;
                 }
             }
             if (hs == 0 && t == 0) { Carry[row0 + g] = run[0]; Carry[row0 + g + 8] = run[1]; }
-        }
-        {   // A0[j] = sum_i ET_new[j][i] S0[i][j]; this warp: value columns 32*hs .. 32*hs+31
-            float Td[4][4];
-            tmem_ld_tiles<4>(Td, tmET + 32 * hs + lane_off);
-            tmem_wait_ld();
-            float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int i = 32 * hs + nt * 8 + 2 * t + e;
-                    acc0 = fmaf(Td[nt][e], *reinterpret_cast<const float*>(S0 + sw(i, row0 + g, HALF64)), acc0);
-                    acc1 = fmaf(Td[nt][2 + e], *reinterpret_cast<const float*>(S0 + sw(i, row0 + g + 8, HALF64)), acc1);
-                }
-            acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-            acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-            if (t == 0) { A0p[hs * 64 + row0 + g] = acc0; A0p[hs * 64 + row0 + g + 8] = acc1; }
         }
         __syncthreads();
         WKV7_PHASE(13);  // epilogue part 1
@@ -447,11 +458,24 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int tt = 16 * hs + nt * 8 + 2 * t + e;
-                    const float lam = Lam[tt * 64 + j], lamp = tt > 0 ? Lam[(tt - 1) * 64 + j] : 0.f;
-                    const float sg = (lam - lamp) * (1.f / kWScale2);
-                    const float glog = a0 - pre[h][nt][e] - adA[h][nt][e];
-                    if (tt < valid) dw_[tok0 + (i64)(c * LC + tt) * C + j] = __float2bfloat16_rn(glog * kWScale * sg * (1.f - sg));
+                    stg[4][tt * 72 + j] = __float2bfloat16_rn((a0 - gl[h][nt][e]) * fw[h][nt][e]);
                 }
+        }
+        {   // dr, da, dk, db out: thread = (token, 16-byte piece)
+            const int tt = tid >> 3, piece = tid & 7;
+            if (tt < valid) {
+                const i64 o = tok0 + (i64)(c * LC + tt) * C + piece * 8;
+                *reinterpret_cast<uint4*>(dr_ + o) = *reinterpret_cast<const uint4*>(stg[0] + tt * 72 + piece * 8);
+                *reinterpret_cast<uint4*>(da_ + o) = *reinterpret_cast<const uint4*>(stg[1] + tt * 72 + piece * 8);
+                *reinterpret_cast<uint4*>(dk_ + o) = *reinterpret_cast<const uint4*>(stg[2] + tt * 72 + piece * 8);
+                *reinterpret_cast<uint4*>(db_ + o) = *reinterpret_cast<const uint4*>(stg[3] + tt * 72 + piece * 8);
+            }
+        }
+        __syncthreads();
+        {
+            const int tt = tid >> 3, piece = tid & 7;
+            if (tt < valid)
+                *reinterpret_cast<uint4*>(dw_ + tok0 + (i64)(c * LC + tt) * C + piece * 8) = *reinterpret_cast<const uint4*>(stg[4] + tt * 72 + piece * 8);
         }
         WKV7_PHASE(14);  // dw out
     }
@@ -474,6 +498,8 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmE) : "memory");
 }
+
+WKV7_PHASE_READER(rwkvb200_phase_clocks_l32_bwd)
 
 }  // namespace v7x
 

@@ -138,7 +138,6 @@ wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         __syncthreads();
         tc_fence_after();
         WKV7_PHASE(12);  // barrier
-        if (c + 1 < nchunks) fetch_chunk<6, FTPW>(raw, src, tok0, C, c + 1, T, warp, lane);
         WKV7_PHASE(2);   // barrier, fetch issue
         // ---- 2. U ------------------------------------------------------------------------------------
         if (warp == 0) {
@@ -200,7 +199,8 @@ wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             mma_commit(bar + 2, lead);
             if (cs.fail) fail = 4;
         }
-        WKV7_PHASE(6);   // issue of the chain
+        if (c + 1 < nchunks) fetch_chunk<6, FTPW>(raw, src, tok0, C, c + 1, T, warp, lane);   // under the chain
+        WKV7_PHASE(6);   // issue of the chain, request of the next chunk
         // ---- 5. y out, state scaled -------------------------------------------------------------------
         if (!mbar_wait(bar + 1, par)) fail = 2;
         tc_fence_after();
