@@ -49,6 +49,7 @@ constexpr int HALF64 = 64 * 128;  // bytes of one 32-column half of a 64-row arr
 constexpr int HALF32 = 32 * 128;  // ... of a 32-row array
 constexpr int ARR64 = 2 * HALF64; // a [64][64] operand array
 constexpr int ARR32 = 2 * HALF32; // a [32][64] operand array
+constexpr int LAMP = 68;          // pitch (floats) of the plain [32][.] array of cumulative log2-decays
 constexpr int UPITCH = 36;        // pitch (floats) of the plain fp32 32x32 matrices (rows 16-byte aligned)
 
 // byte offset of element (row, col) of a swizzled operand array whose halves are `half` bytes apart
@@ -171,7 +172,7 @@ __device__ __forceinline__ void fetch_chunk(RawChunk<NX, TPW>& rc, const bf16* c
 // Writes the scaled operands of the chunk:
 //   AR rows 0-31 = a~_t, rows 32-63 = r~_t        BK rows 0-31 = b~_t, rows 32-63 = k~_t      (columns = key channel)
 //   V rows = v_t (dst_v, a 32-row half-array pair at the given half stride), optionally dY the same way,
-//   We[j] = decay over the whole chunk, and optionally the cumulative log2-decays lam[t][j] (plain [32][64]).
+//   We[j] = decay over the whole chunk, and optionally the cumulative log2-decays lam[t][j] (plain [32][LAMP]).
 // Tokens at or beyond `valid` (counted inside the chunk) are neutral: no decay, zero vectors.
 // Hs is a [NW][64] exchange buffer.  Contains one CTA-wide barrier; the caller synchronises afterwards.
 template <int NX, int TPW, int NW>
@@ -216,7 +217,7 @@ __device__ __forceinline__ void prepare_operands(const RawChunk<NX, TPW>& rc, in
         if constexpr (NX > 6) {
             *reinterpret_cast<float2*>(dstDY + sw(tt, j0, halfDY)) = bf16x2_to_f2(rc.x[6][q]);
         }
-        if (lam_out != nullptr) *reinterpret_cast<float2*>(lam_out + tt * 64 + j0) = make_float2(lam0, lam1);
+        if (lam_out != nullptr) *reinterpret_cast<float2*>(lam_out + tt * LAMP + j0) = make_float2(lam0, lam1);
         wp0 = wt0; wp1 = wt1;
     }
 }

@@ -43,8 +43,8 @@ struct BwdSmemX {
     static constexpr int kD0 = kUkr + HALF32;
     static constexpr int kP = kUak;
     static constexpr int kN1 = kD0 + HALF32;             // [32][32]
-    static constexpr int kLam = kN1 + HALF32;            // plain [32][64]: cumulative log2 decays
-    static constexpr int kWe = kLam + 32 * 64 * 4;       // [64]
+    static constexpr int kLam = kN1 + HALF32;            // plain [32][LAMP]: cumulative log2 decays
+    static constexpr int kWe = kLam + 32 * LAMP * 4;     // [64]
     static constexpr int kA0 = kWe + 256;                // [2][64] partial anchors
     static constexpr int kCarry = kA0 + 512;             // [64] sum of c over the first 16 tokens
     static constexpr int kBar = kCarry + 256;            // 7 mbarriers + tmem slot
@@ -420,7 +420,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                         const float ada = at * gA[nt][x];
                         ct[h][e] = rt * gR[nt][x] + ada - bt * gB[nt][x] - kt * gK[nt][x];
                         gl[h][nt][e] = ada;
-                        const float lam = Lam[tt * 64 + j], lamp = tt > 0 ? Lam[(tt - 1) * 64 + j] : 0.f;
+                        const float lam = Lam[tt * LAMP + j], lamp = tt > 0 ? Lam[(tt - 1) * LAMP + j] : 0.f;
                         const float wt = fex2(lam), iw = fex2(-lam), wp = fex2(lamp);
                         const float sg = (lam - lamp) * (1.f / kWScale2);
                         fw[h][nt][e] = kWScale * sg * (1.f - sg);
