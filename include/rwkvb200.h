@@ -7,8 +7,11 @@
  *
  * Conventions
  *   - plain device pointers and sizes only; all tensors contiguous row-major;
- *   - all buffers are caller-owned; the library keeps no state between calls and
- *     allocates nothing;
+ *   - all buffers are caller-owned and the library allocates nothing.  What it keeps between calls:
+ *     the RWKV-7 kernel choice (rwkvb200_wkv7_select_path, process-wide, atomic), a sticky
+ *     per-device status word written by the tcgen05 kernels when a bounded wait runs out
+ *     (rwkvb200_device_status / _clear), per-stream flag slots of the chunked RWKV-5/6 kernels and
+ *     the fixed scratch array of rwkvb200_wkv6_backward_noalloc;
  *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
  *     kernels are enqueued, not waited for;
  *   - return value: RWKVB200_OK or a negative RWKVB200_E* code; nothing aborts, nothing
@@ -202,18 +205,25 @@ int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len,
                            void* da, void* db, void* stream);
 
 /* Kernel choice for RWKV-7 (process-wide; set it before launching work, not concurrently with it):
- * 0 = automatic (for bf16, N=64, chunk_len=16: setting 3, with the kernels of setting 5 for small
- *     launches (forward: B*H up to twice the number of SMs, backward: up to the number of SMs);
- *     general-shape kernels otherwise),
- * 1 = general-shape kernels only, 2 = mma.sync tensor-core kernels, 3 = tcgen05 forward with the
- * mma.sync backward, 4 = tcgen05 forward and backward, 5 = the producer/consumer forms of the
- * tcgen05 forward and the mma.sync backward (2 to 5 refuse other shapes).
- * The forward and the backward of one operator call must run under the same setting: the
- * layout of s / sa differs between the two kernel families.  No counterpart in the reference. */
+ * 0 = automatic (tensor-core kernels for bf16, N=64, chunk_len=16; general-shape kernels otherwise),
+ * 1 = general-shape kernels only, 2 = tensor-core kernels or RWKVB200_EUNSUPPORTED.
+ * The forward and the backward of one operator call must run under the same setting: the content
+ * of s / sa differs between the two kernel families (tensor-core kernels: s[b][h][c] = state at the
+ * start of 32-token chunk c, c < ceil(T/32), the rest of s and all of sa untouched; general-shape
+ * kernels: transposed state at the end of every chunk_len tokens, and sa).  No counterpart in the
+ * reference. */
 int rwkvb200_wkv7_select_path(int path);
-/* Synchronises the device and returns the sticky device-side status word: 0, or the index of a
- * bounded wait that expired inside a tcgen05 kernel (its outputs are then invalid). */
+/* Synchronous read of the current device's sticky status word: 0, or 10 + n / 20 + n when the n-th
+ * bounded wait of the tensor-core forward / backward ran out in some thread block (the outputs of
+ * that call are then invalid); negative on a CUDA error.  Per device; stays set until cleared. */
 int rwkvb200_device_status(void);
+/* Resets the current device's status word.  No counterpart in the reference. */
+int rwkvb200_device_status_clear(void);
+/* Test hook: the next tensor-core rwkvb200_wkv7_forward call does not issue the first product of its
+ * first chunk and polls for it 2^10 times only, so that the bounded-wait path (status word, release of
+ * tensor memory, orderly return) can be exercised with nothing in flight.  That call's outputs are
+ * invalid.  No counterpart in the reference. */
+int rwkvb200_wkv7_test_expire_next_forward(void);
 
 #ifdef __cplusplus
 }

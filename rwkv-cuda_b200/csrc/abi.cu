@@ -2,6 +2,7 @@
 // between the general-shape kernels and the N = 64 tensor-core path).
 #include "common.cuh"
 #include "wkv7_dispatch.cuh"
+#include <atomic>
 #include <initializer_list>
 
 namespace rwkvb200 {
@@ -44,22 +45,20 @@ extern "C" const char* rwkvb200_last_error(void) { return g_err; }
 extern "C" int rwkvb200_version(void) { return 100; }
 extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 
-// 0 = automatic (= 3 where applicable), 1 = general-shape kernels only, 2 = mma.sync chunked kernels,
-// 3 = tcgen05 forward + chunked backward, 4 = tcgen05 forward and backward,
-// 5 = producer/consumer forms of the tcgen05 forward and the chunked backward.  Automatic takes them
-// instead of 3 for small launches: the forward up to two (batch, head) units per SM, the backward up to one.
-static int g_wkv7_path = 0;
-
-static int sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        return 0;
-    return n;
-}
+// 0 = automatic (tensor-core kernels where the shape allows), 1 = general-shape kernels only,
+// 2 = tensor-core kernels or an error.  Read once per call; forward and backward of one operator call
+// must see the same value (the saved buffers differ between the two kernel families).
+static std::atomic<int> g_wkv7_path{0};
+static std::atomic<int> g_wkv7_test_expire{0};
 
 extern "C" int rwkvb200_wkv7_select_path(int path) {
-    RWKV_REQUIRE(path >= 0 && path <= 6, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..6", path);
-    g_wkv7_path = path;
+    RWKV_REQUIRE(path >= 0 && path <= 2, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..2", path);
+    g_wkv7_path.store(path);
+    return RWKVB200_OK;
+}
+
+extern "C" int rwkvb200_wkv7_test_expire_next_forward(void) {
+    g_wkv7_test_expire.store(1);
     return RWKVB200_OK;
 }
 
@@ -70,12 +69,13 @@ static bool aligned16(std::initializer_list<const void*> ps) {
 }
 
 // Forward and backward must agree on the layout of the saved buffers, so the choice depends
-// on (dtype, N, chunk_len) only; misaligned tensors on the tensor-core path are an error.
-static int wkv7_use_chunked(const char* what, int dtype, int N, int chunk, bool* use) {
+// on (path, dtype, N, chunk_len) only; misaligned tensors on the tensor-core path are an error.
+static int wkv7_use_tensor_path(const char* what, int dtype, int N, int chunk, bool* use) {
+    const int path = g_wkv7_path.load();
     const bool shape_ok = dtype == RWKVB200_BF16 && N == 64 && chunk == 16;
-    if (g_wkv7_path >= 2)
+    if (path == 2)
         RWKV_REQUIRE(shape_ok, RWKVB200_EUNSUPPORTED, "%s: tensor-core path needs bf16, N=64, chunk_len=16", what);
-    *use = shape_ok && g_wkv7_path != 1;
+    *use = shape_ok && path != 1;
     return RWKVB200_OK;
 }
 
@@ -91,11 +91,18 @@ static int wkv7_check(const char* what, int dtype, int B, int T, int H, int N, i
 }
 
 extern "C" int rwkvb200_device_status(void) {
-    if (const int f = wkv7_umma_error()) return f;
-    if (const int f = wkv7_l32_fwd_error()) return 10 + f;
-    if (const int f = wkv7_l32_bwd_error()) return 20 + f;
-    if (const int f = wkv7_umma_split_error()) return f;
-    return wkv7_umma_bwd_error();
+    const int f = wkv7_l32_fwd_error(), g = wkv7_l32_bwd_error();
+    if (f < 0 || g < 0) {
+        set_error("device_status: reading the status words failed");
+        return RWKVB200_ECUDA;
+    }
+    if (f) return 10 + f;
+    return g ? 20 + g : 0;
+}
+
+extern "C" int rwkvb200_device_status_clear(void) {
+    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
+    return RWKVB200_OK;
 }
 
 extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int chunk_len, const float* s0,
@@ -106,21 +113,12 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
     RWKV_NOTNULL(y);
     RWKV_REQUIRE((s == nullptr) == (sa == nullptr), RWKVB200_EINVAL,
                  "wkv7_forward: s and sa must be given together (or both NULL for inference)");
-    bool chunked;
-    if (int e = wkv7_use_chunked("wkv7_forward", dtype, N, chunk_len, &chunked)) return e;
-    if (chunked) {
+    bool tensor;
+    if (int e = wkv7_use_tensor_path("wkv7_forward", dtype, N, chunk_len, &tensor)) return e;
+    if (tensor) {
         RWKV_REQUIRE(aligned16({s0, r, w, k, v, a, b, y, sT, s, sa}), RWKVB200_EALIGN,
                      "wkv7_forward: the bf16 N=64 path needs 16-byte aligned tensors");
-        // up to two units per SM: the time is (close to) one unit's chain of chunks, which the
-        // producer/consumer kernel shortens (it fits two CTAs per SM); with more units per SM four plain
-        // CTAs per SM give more throughput (B=4 at H=64: 0.72 vs 0.78 ms; B=8: 1.41 vs 1.34 ms)
-        if (g_wkv7_path == 6)
-            return wkv7_l32_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
-        if (g_wkv7_path == 5 || (g_wkv7_path == 0 && (long long)B * H <= 2LL * sm_count()))
-            return wkv7_umma_split_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
-        if (g_wkv7_path != 2)   // automatic, 3 and 4: the tcgen05 forward
-            return wkv7_umma_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
-        return wkv7_chunked_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
+        return wkv7_l32_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, g_wkv7_test_expire.exchange(0), as_stream(stream));
     }
     return wkv7_generic_forward(dtype, B, T, H, N, chunk_len, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
 }
@@ -133,23 +131,12 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
     RWKV_NOTNULL(r); RWKV_NOTNULL(w); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(a); RWKV_NOTNULL(b);
     RWKV_NOTNULL(dy); RWKV_NOTNULL(s); RWKV_NOTNULL(sa);
     RWKV_NOTNULL(dr); RWKV_NOTNULL(dw); RWKV_NOTNULL(dk); RWKV_NOTNULL(dv); RWKV_NOTNULL(da); RWKV_NOTNULL(db);
-    bool chunked;
-    if (int e = wkv7_use_chunked("wkv7_backward", dtype, N, chunk_len, &chunked)) return e;
-    if (chunked) {
+    bool tensor;
+    if (int e = wkv7_use_tensor_path("wkv7_backward", dtype, N, chunk_len, &tensor)) return e;
+    if (tensor) {
         RWKV_REQUIRE(aligned16({r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db}), RWKVB200_EALIGN,
                      "wkv7_backward: the bf16 N=64 path needs 16-byte aligned tensors");
-        if (g_wkv7_path == 6)
-            return wkv7_l32_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, ds0, dr, dw, dk, dv, da, db, as_stream(stream));
-        if (g_wkv7_path == 4)
-            return wkv7_umma_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
-                                      as_stream(stream));
-        // one unit per SM or fewer: the time is one unit's chain of chunks, which the producer/consumer
-        // kernel shortens; with more units per SM two plain CTAs per SM give more throughput
-        if (g_wkv7_path == 5 || (g_wkv7_path == 0 && (long long)B * H <= sm_count()))
-            return wkv7_split_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
-                                       as_stream(stream));
-        return wkv7_chunked_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db,
-                                     as_stream(stream));
+        return wkv7_l32_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, ds0, dr, dw, dk, dv, da, db, as_stream(stream));
     }
     return wkv7_generic_backward(dtype, B, T, H, N, chunk_len, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv,
                                  da, db, as_stream(stream));

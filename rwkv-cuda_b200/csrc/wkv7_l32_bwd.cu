@@ -117,7 +117,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     const i64 tok0 = (i64)bb * T * C + hh * 64;
     const i64 sbase = (i64)(bb * H + hh) * 64 * 64;
     const int nchunks = (T + LC - 1) / LC;
-    const float* ck = ck_ + (i64)(bb * H + hh) * nchunks * 64 * 64;
+    const float* ck = ck_ + (i64)(bb * H + hh) * (T / 16) * 64 * 64;   // block [b][h] of the caller's (B,H,T/16,N,N) buffer
     const bf16* src[7] = {r_, w_, k_, v_, a_, b_, dy_};
 
     if (tid == 0) {
@@ -515,6 +515,11 @@ int wkv7_l32_backward(int B, int T, int H, const void* r, const void* w, const v
                                                                dsT, s, ds0, (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv,
                                                                (bf16*)da, (bf16*)db);
     return check_launch("wkv7_backward(tcgen05, 32-token chunks)");
+}
+
+int wkv7_l32_bwd_error_clear() {
+    const int z = 0;
+    return cudaMemcpyToSymbol(v7x::g_l32_bwd_error, &z, sizeof(int)) == cudaSuccess ? 0 : -1;
 }
 
 int wkv7_l32_bwd_error() {

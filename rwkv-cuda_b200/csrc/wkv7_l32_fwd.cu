@@ -16,7 +16,7 @@
 // Tensor memory: 128 columns (S | U then X) + 32 columns (SA), as two allocations; three CTAs use 480
 // of the SM's 512 columns, and shared memory (69 KB) keeps a fourth CTA away.
 // Saved for the backward: the state at the start of every 32-token chunk, [chunk][i][j] per
-// (batch, head), in the first half of the caller's `s` buffer; `sa` is not used.
+// (batch, head), as s[b][h][c] of the caller's (B,H,T/16,64,64) buffer, c < ceil(T/32); `sa` is not used.
 // T may be any multiple of 16: a last half chunk is padded with neutral tokens.
 #include "wkv7_l32.cuh"
 #include "wkv7_dispatch.cuh"
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(FNT, 3)
 wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __restrict__ r_,
                      const bf16* __restrict__ w_, const bf16* __restrict__ k_, const bf16* __restrict__ v_,
                      const bf16* __restrict__ a_, const bf16* __restrict__ b_, bf16* __restrict__ y_,
-                     float* __restrict__ sT_, float* __restrict__ ck_, float* __restrict__ dbg_) {
+                     float* __restrict__ sT_, float* __restrict__ ck_, int test_expire) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // the swizzle acts on address bits
     unsigned char *AR = smem + FwdSmem::kAR, *BK = smem + FwdSmem::kBK, *Vs = smem + FwdSmem::kV;
@@ -73,7 +73,7 @@ wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     const i64 tok0 = (i64)bb * T * C + hh * 64;
     const i64 sbase = (i64)(bb * H + hh) * 64 * 64;
     const int nchunks = (T + LC - 1) / LC;
-    float* ck = ck_ ? ck_ + (i64)(bb * H + hh) * nchunks * 64 * 64 : nullptr;
+    float* ck = ck_ ? ck_ + (i64)(bb * H + hh) * (T / 16) * 64 * 64 : nullptr;   // block [b][h] of the caller's (B,H,T/16,N,N) buffer
     const bf16* src[6] = {r_, w_, k_, v_, a_, b_};
 
     if (tid == 0) {
@@ -140,11 +140,11 @@ wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         WKV7_PHASE(12);  // barrier
         WKV7_PHASE(2);   // barrier, fetch issue
         // ---- 2. U ------------------------------------------------------------------------------------
-        if (warp == 0) {
+        if (warp == 0 && !(test_expire && c == 0)) {
             issue_u(tmX, arA, bkA, lead);
             mma_commit(bar, lead);
         }
-        if (!mbar_wait(bar, par)) fail = 1;
+        if (!mbar_wait(bar, par, test_expire ? (1 << 10) : (1 << 20))) fail = 1;
         tc_fence_after();
         WKV7_PHASE(3);   // U on the tensor core
         // ---- 3. masked U, inverse ----------------------------------------------------------------------
@@ -163,14 +163,6 @@ wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         __syncthreads();
         tc_fence_after();
         WKV7_PHASE(5);   // inverse
-#ifdef RWKVB200_DEBUG_DUMP
-        if (dbg_ != nullptr && c == 0 && blockIdx.x == 0 && blockIdx.y == 0)
-            for (int i = tid; i < 1024; i += FNT) {
-                dbg_[i] = *reinterpret_cast<float*>(N1 + sw32(i >> 5, i & 31));
-                dbg_[1024 + i] = *reinterpret_cast<float*>(D0 + sw32(i >> 5, i & 31));
-                dbg_[2048 + i] = Uab[(i >> 5) * UPITCH + (i & 31)];
-            }
-#endif
         // ---- 4. the dependent chain --------------------------------------------------------------------
         if (warp == 0) {
             const uint32_t id64 = idesc64(64, 0, 0);
@@ -265,14 +257,21 @@ WKV7_PHASE_READER(rwkvb200_phase_clocks_l32_fwd)
 }  // namespace v7x
 
 int wkv7_l32_forward(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k, const void* v,
-                     const void* a, const void* b, void* y, float* sT, float* s, float* sa, cudaStream_t st) {
+                     const void* a, const void* b, void* y, float* sT, float* s, int test_expire, cudaStream_t st) {
     using namespace v7x;
     cudaError_t e = cudaFuncSetAttribute(wkv7x_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv7_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     dim3 grid(H, B);
     wkv7x_forward_kernel<<<grid, FNT, FwdSmem::kBytes, st>>>(T, H, s0, (const bf16*)r, (const bf16*)w, (const bf16*)k,
-                                                            (const bf16*)v, (const bf16*)a, (const bf16*)b, (bf16*)y, sT, s, sa);
+                                                            (const bf16*)v, (const bf16*)a, (const bf16*)b, (bf16*)y, sT, s, test_expire);
     return check_launch("wkv7_forward(tcgen05, 32-token chunks)");
+}
+
+int wkv7_l32_bwd_error_clear();
+int wkv7_l32_clear_errors() {
+    const int z = 0;
+    if (cudaMemcpyToSymbol(v7x::g_l32_fwd_error, &z, sizeof(int)) != cudaSuccess) return -1;
+    return wkv7_l32_bwd_error_clear();
 }
 
 int wkv7_l32_fwd_error() {

@@ -9,9 +9,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[2, 3, 4, 5], ids=["mma_sync", "tcgen05_fwd", "tcgen05_fwd_bwd", "producer_consumer"])
+@pytest.fixture(params=[2, 0], ids=["forced", "automatic"])
 def R(request):
-    """2 = mma.sync chunked kernels, 3 = tcgen05 forward with the same backward."""
+    """2 = tensor-core kernels or an error, 0 = automatic choice (the same kernels for these shapes)."""
     import rwkv_cuda_b200 as R
     from rwkv_cuda_b200 import _lib
     _lib.call("rwkvb200_wkv7_select_path", request.param)
@@ -20,7 +20,7 @@ def R(request):
     assert _lib.lib().rwkvb200_device_status() == 0, "a bounded wait expired inside a tcgen05 kernel"
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 16, 1), (2, 64, 2), (1, 512, 3)])
+@pytest.mark.parametrize("B,T,H", [(1, 16, 1), (1, 32, 1), (1, 48, 2), (2, 64, 2), (1, 512, 3)])
 @pytest.mark.parametrize("use_s0", [True, False])
 def test_forward(R, B, T, H, use_s0):
     N = 64
@@ -38,8 +38,8 @@ def test_forward(R, B, T, H, use_s0):
     torch.cuda.synchronize()
     print("y", Hh.assert_close(y, y64, Hh.TOL_BF16, "y"))
     print("sT", Hh.assert_close(sT, sT64, Hh.TOL_BF16, "sT"))
-    assert torch.isfinite(s).all() and torch.isfinite(sa).all()
-    # saved state of chunk 0 is the initial state
+    # saved: the state at the start of every 32-token chunk; chunk 0 holds the initial state
+    assert torch.isfinite(s[:, :, : (T + 31) // 32]).all()
     want0 = inp["s0"] if use_s0 else torch.zeros(B, H, N, N)
     assert torch.equal(s[:, :, 0].cpu(), want0)
 
@@ -64,7 +64,7 @@ def _run_both(R, inp, H, use_s0, use_sT):
     return dict(y=y, sT=sT, ds0=ds0, **dict(zip(("dr", "dw", "dk", "dv", "da", "db"), g)))
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 16, 1), (2, 64, 2), (1, 512, 3), (1, 2048, 1)])
+@pytest.mark.parametrize("B,T,H", [(1, 16, 1), (1, 48, 2), (2, 64, 2), (1, 512, 3), (1, 2048, 1)])
 @pytest.mark.parametrize("use_s0,use_sT", [(True, True), (False, False), (True, False)])
 def test_forward_backward(R, B, T, H, use_s0, use_sT):
     N = 64
@@ -83,20 +83,39 @@ def _set_path(p):
     _lib.call("rwkvb200_wkv7_select_path", p)
 
 
-@pytest.mark.parametrize("B,T,H", [(1, 64, 3), (3, 32, 64), (5, 32, 64)])
-def test_kernel_choice_by_grid_size_is_bit_exact(B, T, H):
-    """The producer/consumer kernels (small grids) and the plain ones (B*H above the SM count) do the
-    same arithmetic in the same order: forced either way, and chosen automatically on both sides of
-    the threshold, they must agree bit for bit."""
+def test_results_do_not_depend_on_the_grid():
+    """A (batch, head) unit is computed by one thread block on its own: its results are bit-identical
+    whether it runs alone or among 320 units (more than one per SM, several per SM in flight)."""
     import rwkv_cuda_b200 as R
-    inp = Hh.v7_inputs(B, T, H, 64, seed=11)
-    outs = {}
-    try:
-        for p in (3, 5, 0):
-            _set_path(p)
-            outs[p] = _run_both(R, inp, H, True, True)
-    finally:
-        _set_path(0)
-    for n in ("y", "sT", "dr", "dw", "dk", "dv", "da", "db", "ds0"):
-        assert torch.equal(outs[3][n], outs[5][n]), n
-        assert torch.equal(outs[3][n], outs[0][n]), n
+    H, T = 64, 64
+    big = Hh.v7_inputs(5, T, H, 64, seed=11)
+    out_big = _run_both(R, big, H, True, True)
+    b, h = 3, 17
+    one = {n: (x[b : b + 1, :, h * 64 : (h + 1) * 64] if x.dim() == 3 else x[b : b + 1, h : h + 1]).contiguous() for n, x in big.items()}
+    out_one = _run_both(R, one, 1, True, True)
+    for n in ("y", "dr", "dw", "dk", "dv", "da", "db"):
+        assert torch.equal(out_big[n][b, :, h], out_one[n][0, :, 0]), n
+    for n in ("sT", "ds0"):
+        assert torch.equal(out_big[n][b, h], out_one[n][0, 0]), n
+
+
+def test_bounded_wait_runs_out_and_the_library_recovers():
+    """With the test hook the first product of the next forward is not issued, so the wait for it runs
+    out (nothing is in flight): the kernel records its status, releases tensor memory and returns; after
+    a reset the next call is correct again."""
+    import rwkv_cuda_b200 as R
+    from rwkv_cuda_b200 import _lib
+    L = _lib.lib()
+    assert L.rwkvb200_device_status() == 0
+    inp = Hh.v7_inputs(1, 64, 2, 64, seed=3)
+    good = _run_both(R, inp, 2, True, True)
+    _lib.call("rwkvb200_wkv7_test_expire_next_forward")
+    _run_both(R, inp, 2, True, True)
+    assert L.rwkvb200_device_status() == 11
+    assert L.rwkvb200_device_status() == 11, "the status word is sticky"
+    _lib.call("rwkvb200_device_status_clear")
+    assert L.rwkvb200_device_status() == 0
+    again = _run_both(R, inp, 2, True, True)
+    for n in good:
+        assert torch.equal(good[n], again[n]), n
+    assert L.rwkvb200_device_status() == 0
