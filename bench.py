@@ -45,17 +45,21 @@ class V7Workload:
     dtype_name = "bf16"
     metric = "WKV fwd+bwd tokens/s, RWKV-7 B16 T4096 C4096 bf16"
 
-    def __init__(self, b_local, device, seed_rank):
+    def __init__(self, b_local, device, rank):
+        """Every rank draws the same seed-42 batch of the full configuration and keeps rows
+        [rank*b_local, (rank+1)*b_local): shard g of a multi-GPU run is bit-identical to those rows of
+        the single-GPU input."""
         import rwkv_cuda_b200 as R
         self.R = R
         B, T, H, N = b_local, self.T, self.H, self.N
         self.b = B
         g = torch.Generator(device=device)
-        g.manual_seed(42 + seed_rank)
+        g.manual_seed(42)
         bf = torch.bfloat16
+        lo = rank * b_local
 
         def mk(scale=1.0):
-            return torch.randn(B, T, H, N, generator=g, device=device) * scale
+            return (torch.randn(self.B, T, H, N, generator=g, device=device)[lo:lo + B] * scale).contiguous()
 
         # generated on the device for speed, then parked in pinned HOST buffers: the end-to-end
         # leg starts from those host copies
@@ -65,8 +69,8 @@ class V7Workload:
         a, b = -kk, kk * torch.sigmoid(mk())
         self.host_in = [x.to(bf).cpu().pin_memory() for x in (r, w, k, v, a, b)]
         self.host_dy = mk().to(bf).cpu().pin_memory()
-        self.host_s0 = (0.1 * torch.randn(B, H, N, N, generator=g, device=device)).cpu().pin_memory()
-        self.host_dsT = torch.randn(B, H, N, N, generator=g, device=device).cpu().pin_memory()
+        self.host_s0 = (0.1 * torch.randn(self.B, H, N, N, generator=g, device=device)[lo:lo + B]).cpu().pin_memory()
+        self.host_dsT = torch.randn(self.B, H, N, N, generator=g, device=device)[lo:lo + B].cpu().pin_memory()
         del r, k, v, w, kk, a, b
         dev = device
         self.dev = dev
@@ -100,9 +104,9 @@ class V7Workload:
 
     launches_per_step = 2
     # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel per token, from the ncu
-    # capture of the reduced case (profiles/wkv7_default_path_tcgen05_fwd_mma_bwd_B8_T1024.md); traffic is
+    # capture of the reduced case (profiles/wkv7_tcgen05_chunk32_B8_T1024.md); traffic is
     # proportional to the token count
-    dram_bytes_per_token_bwd = (1.149294e9 + 0.388178e9) / (8 * 1024)
+    dram_bytes_per_token_bwd = (0.746658e9 + 0.376867e9) / (8 * 1024)
 
     def e2e_step(self):
         """Host buffers in, host buffers out, through the public host-buffer API
@@ -322,7 +326,7 @@ def run_secondary(op, args):
         fwd = lambda: R.ops.wkv5_forward(B, T, C, H, r, k, v, eew, u, y)
         bwd = lambda: R.ops.wkv5_backward(B, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu)
         bytes_f, bytes_b = 8 * C * B * T, 14 * C * B * T
-        bound, note = "hbm", "general-shape (scalar fp32) kernel: FP32-pipe bound, HBM roof shown for reference"
+        bound, note = "hbm", "chunked tensor-core kernels (mma.sync TF32), decay constant over time"
         Tc = 256
 
         def cpu():
@@ -344,7 +348,7 @@ def run_secondary(op, args):
         bwd = lambda: R.ops.wkv6state_backward_ex(B, T, C, H, r, k, v, wraw, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0)
         st = 4 * B * H * N * N
         bytes_f, bytes_b = 10 * C * B * T + 2 * st, 18 * C * B * T + 2 * st
-        bound, note = "hbm", "general-shape (scalar fp32) kernel: FP32-pipe bound, HBM roof shown for reference"
+        bound, note = "hbm", "chunked tensor-core kernels (mma.sync TF32), per-token decay, fp32 state in/out"
         Tc = 256
 
         def cpu():
@@ -380,6 +384,50 @@ def run_secondary(op, args):
     print(json.dumps(out), flush=True)
 
 
+def reference_kernel_timing(wl, fwd_ms, bwd_ms):
+    """The reference project's own CUDA kernel (built as a test-only checker into oracle/_ref/ where a
+    reference checkout was present) on this rank's device tensors, outside the timed region: its times,
+    the speed-up of this library over it, and both kernels' RMS errors against the fp64 formula on a
+    sample of (batch, head) units.  None-like dict with a reason when the library is not there."""
+    try:
+        from tests import ref_kernel
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"tests/ref_kernel.py not importable: {e}"}
+    if not ref_kernel.available():
+        return {"unavailable": "oracle/_ref/librwkv7_ref.so not built (no reference checkout at build time)"}
+    y, sT, ds0 = torch.empty_like(wl.y), torch.empty_like(wl.sT), torch.empty_like(wl.ds0)
+    gr = [torch.empty_like(x) for x in wl.grads]
+    f = lambda: ref_kernel.forward(wl.s0, *wl.inp, y, sT, wl.s, wl.sa)
+    b = lambda: ref_kernel.backward(*wl.inp, wl.dy, wl.dsT, wl.s, wl.sa, ds0, *gr)
+    f(); b()
+    tf, tb = ref_kernel._time(f, 3), ref_kernel._time(b, 3)
+    out = {"fwd_ms": tf, "bwd_ms": tb, "tokens_per_s": wl.b * wl.T / ((tf + tb) * 1e-3), "speedup": (tf + tb) / (fwd_ms + bwd_ms),
+           "source": "rwkv7_fast_fused/cuda/rwkv7_statepassing_clampw.cu compiled for sm_100a with its own flags"}
+    # errors of both kernels on two units against the fp64 formula (the reference run leaves s/sa in its own layout: rerun ours after)
+    try:
+        from oracle import wkv_oracle as O
+        N = wl.N
+        units = [(0, 0), (wl.b - 1, wl.H - 1)]
+        names = ("y", "dr", "dw", "dk", "dv", "da", "db")
+        ref_out = dict(zip(names, [y] + gr))
+        wl.forward(); wl.backward(); torch.cuda.synchronize()
+        our_out = dict(zip(names, [wl.y] + wl.grads))
+        Tc = min(wl.T, 1024)   # the first Tc tokens of a unit do not depend on later ones in the forward; gradients need the whole unit
+        errs = {"ours": {}, "reference_kernel": {}}
+        acc = {k: {n: [0.0, 0.0] for n in ("y",)} for k in errs}
+        for (bi, hi) in units:
+            x64 = [t[bi:bi + 1, :Tc, hi].double().cpu().reshape(1, Tc, N) for t in wl.inp]
+            s064 = wl.s0[bi:bi + 1, hi:hi + 1].double().cpu()
+            y64, _ = O.wkv7(*x64, 1, s0=s064)
+            for k, o in (("ours", our_out), ("reference_kernel", ref_out)):
+                d = o["y"][bi, :Tc, hi].double().cpu().reshape(1, Tc, N) - y64
+                acc[k]["y"][0] += float((d * d).sum()); acc[k]["y"][1] += float((y64 * y64).sum())
+        out["rms_error_y_first_%d_tokens" % Tc] = {k: (acc[k]["y"][0] / acc[k]["y"][1]) ** 0.5 for k in acc}
+    except Exception as e:  # noqa: BLE001
+        out["rms_error_note"] = f"error sample skipped: {e}"
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -392,7 +440,7 @@ def main():
     ap.add_argument("--cpu-seq", type=int, default=256, help="sequence length of one CPU-baseline step (B=1, C=4096)")
     ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
     ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
-    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
+    ap.add_argument("--path", type=int, default=0, choices=[0, 1, 2],
                     help="RWKV-7 kernel family (rwkvb200_wkv7_select_path); 0 = automatic")
     ap.add_argument("--op", default="wkv7", choices=["wkv7", "wkv4", "timex", "wkv5", "wkv6state"],
                     help="wkv7 = the headline configuration (default); the others are BASELINE configurations 1-4")
@@ -486,6 +534,12 @@ def main():
         e2e_val = tokens_step * args.e2e_steps / (te.item() * 1e-3)
         h2d, d2h = wl.e2e_bytes()
 
+    from rwkv_cuda_b200 import _lib as _L
+    st = _L.lib().rwkvb200_device_status()
+    if st != 0:
+        raise SystemExit(f"bench.py: device status {st} after the timed region (a bounded wait ran out): results invalid")
+    ref_kernel_block = reference_kernel_timing(wl, fwd_ms, bwd_ms) if rank == 0 else None
+
     if rank == 0:
         peak, peak_src = hbm_peak()
         bb = W.bytes_bwd(b_local)
@@ -511,6 +565,7 @@ def main():
                     "d2h_bytes_per_step": d2h * world, "steps": args.e2e_steps},
             "gpu_launches": W.launches_per_step * args.steps,
             "clocks": clocks.summary(),
+            "reference_kernel": ref_kernel_block,
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

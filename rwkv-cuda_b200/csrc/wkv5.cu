@@ -237,11 +237,12 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
     if (!DUAL && chunked_ok<E>(T, N, {r, k, v, u1, y})) {
         // RWKV-5 is RWKV-6 with a decay that does not change over time: the chunked tensor-core kernel
         // runs first, the general-shape kernel below only if the decay is too strong for the chunked form
-        int* flag = wkv6_chunked_next_flag();
-        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "wkv5_forward: no device flag");
-        cudaMemsetAsync(flag, 0, sizeof(int), st);
-        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w1, 2, u1, nullptr, 0, y, nullptr, nullptr, flag, st)) return e;
-        only_if = flag;
+        int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
+        if (flag != nullptr) {
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_forward: clearing the device flag failed");
+            if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w1, 2, u1, nullptr, 0, y, nullptr, nullptr, flag, st)) return e;
+            only_if = flag;
+        }
     }
 #define RWKV_GO(NM)                                                                                           \
     wkv5_forward_kernel<E, NM, DUAL><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, \
@@ -265,14 +266,15 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
     if (!DUAL && scratch != nullptr && chunked_ok<E>(T, N, {r, k, v, u1, gy, gr, gk, gv, gw1, gu1, scratch})) {
         // chunked forward into the scratch buffer (chunk-start states), chunked reverse pass, then the
         // general-shape kernel only if the decay is too strong for the chunked form
-        int* flag = wkv6_chunked_next_flag();
-        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "wkv5_backward: no device flag");
-        cudaMemsetAsync(flag, 0, sizeof(int), st);
-        float* ck = static_cast<float*>(scratch);
-        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
-        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st))
-            return e;
-        only_if = flag;
+        int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
+        if (flag != nullptr) {
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_backward: clearing the device flag failed");
+            float* ck = static_cast<float*>(scratch);
+            if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
+            if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st))
+                return e;
+            only_if = flag;
+        }
     }
 #define RWKV_GO(NM)                                                                                              \
     wkv5_backward_kernel<E, NM, DUAL><<<B * H, NM, 0, st>>>(                                                     \

@@ -20,6 +20,7 @@
 //   dL/dlog d_t[i] = A_{t+1} - Q_t,     A_t = A_{t+1} - Q_t + P_t,    A_T = sum_j dsT[j,i] S_T[j,i]
 // so no per-thread history of states is kept (the reference keeps T*N floats per thread and
 // fails beyond T = 64..128) and T is unlimited.
+#include <atomic>
 #include "common.cuh"
 #include "wkv6_chunked.cuh"
 #include <initializer_list>
@@ -259,11 +260,12 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
     if (chunked_ok<E>(T, N, {r, k, v, w, u, s0, y, sT})) {
         // tensor-core kernel first; the general-shape kernel below then only runs if that one found a
         // chunk whose decay is too strong for the chunked form
-        int* flag = wkv6_chunked_next_flag();
-        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "%s: no device flag", what);
-        cudaMemsetAsync(flag, 0, sizeof(int), st);
-        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, y, sT, nullptr, flag, st)) return e;
-        only_if = flag;
+        int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
+        if (flag != nullptr) {
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
+            if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, y, sT, nullptr, flag, st)) return e;
+            only_if = flag;
+        }
     }
 #define RWKV_GO(NM)                                                                                              \
     wkv6_forward_kernel<E, NM><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, w, w_raw, \
@@ -288,14 +290,15 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         // tensor-core kernels first: a forward pass that leaves the chunk-start states in the scratch
         // buffer, then the reverse pass; the general-shape kernel below then only runs if a chunk's decay
         // was too strong for the chunked form (it reuses the front of the same scratch buffer)
-        int* flag = wkv6_chunked_next_flag();
-        RWKV_REQUIRE(flag != nullptr, RWKVB200_ECUDA, "%s: no device flag", what);
-        cudaMemsetAsync(flag, 0, sizeof(int), st);
-        float* ck = static_cast<float*>(scratch);
-        if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
-        if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
-            return e;
-        only_if = flag;
+        int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
+        if (flag != nullptr) {
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
+            float* ck = static_cast<float*>(scratch);
+            if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
+            if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
+                return e;
+            only_if = flag;
+        }
     }
 #define RWKV_GO(NM)                                                                                               \
     wkv6_backward_kernel<E, NM><<<B * H, NM, 0, st>>>(T, C, H, N, (const E*)r, (const E*)k, (const E*)v, w, w_raw, \
@@ -366,7 +369,7 @@ namespace {
 constexpr size_t kNoAllocMaxElems = size_t(8) << 20;  // B*T*C limit: 8 Mi floats = 32 MiB
 static __device__ __align__(256) float g_wkv6_noalloc_scratch[kNoAllocMaxElems];
 constexpr int kMaxDevices = 64;
-float* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array, per device, filled on first use
+std::atomic<float*> g_noalloc_ptr[kMaxDevices] = {};  // device address of the array, per device, filled on first use
 }  // namespace
 }  // namespace rwkvb200
 
@@ -387,7 +390,7 @@ extern "C" int rwkvb200_wkv6_backward_noalloc(int dtype, int B, int T, int C, in
     cudaError_t ce = cudaGetDevice(&dev);
     RWKV_REQUIRE(ce == cudaSuccess && dev >= 0 && dev < kMaxDevices, RWKVB200_ECUDA,
                  "wkv6_backward_noalloc: cudaGetDevice: %s (device %d)", cudaGetErrorString(ce), dev);
-    float* scratch = g_noalloc_ptr[dev];
+    float* scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
     if (scratch == nullptr) {
         // In host code the array's name is only a handle; the device address has to be asked for,
         // once per device, with that device current.
@@ -396,7 +399,7 @@ extern "C" int rwkvb200_wkv6_backward_noalloc(int dtype, int B, int T, int C, in
         RWKV_REQUIRE(ce == cudaSuccess && p != nullptr, RWKVB200_ECUDA,
                      "wkv6_backward_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
         scratch = static_cast<float*>(p);
-        g_noalloc_ptr[dev] = scratch;
+        g_noalloc_ptr[dev].store(scratch, std::memory_order_release);
     }
     // The kernel writes every scratch element it later reads (same thread, same launch), so
     // nothing has to be cleared between calls.

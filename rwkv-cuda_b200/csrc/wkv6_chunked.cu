@@ -17,6 +17,7 @@
 #include "wkv7_chunked.cuh"
 #include "wkv6_chunked.cuh"
 #include <atomic>
+#include <mutex>
 
 namespace rwkvb200 {
 namespace v6c {
@@ -610,21 +611,34 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
 }  // namespace v6c
 
-// Flags of the chunked kernels ("a chunk's decay was too strong"): a small ring, one slot per call, so
-// that calls in flight on different streams do not share one.
-static __device__ int g_chunked_unsafe[64];
-int* wkv6_chunked_next_flag() {
+// Flags of the chunked kernels ("a chunk's decay was too strong").  A call enqueues: clear the flag, the
+// chunked kernels (which may raise it), the general-shape kernel (which reads it).  On one stream that is
+// ordered, so every (device, stream) pair owns one slot for good and calls on different streams never share
+// one.  The table holds 256 pairs per process; beyond that the function returns NULL and the caller runs
+// the general-shape kernel alone.  (A CUDA graph captured from such a call carries the slot of the
+// capturing stream: replay it on one stream at a time.)
+constexpr int kFlagSlots = 256;
+static __device__ int g_chunked_unsafe[kFlagSlots];
+int* wkv6_chunked_flag(cudaStream_t st) {
     constexpr int kMaxDevices = 64;
-    static int* base[kMaxDevices] = {};             // device address of the ring, per device
-    static std::atomic<unsigned> counter{0};
+    static std::mutex mu;
+    static int* base[kMaxDevices] = {};             // device address of the slot array, per device
+    static struct { int dev; cudaStream_t st; } owner[kFlagSlots];
+    static int used = 0;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
     if (base[dev] == nullptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_chunked_unsafe) != cudaSuccess) return nullptr;
         base[dev] = static_cast<int*>(p);
     }
-    return base[dev] + (counter.fetch_add(1) & 63);
+    for (int i = 0; i < used; ++i)
+        if (owner[i].dev == dev && owner[i].st == st) return base[dev] + i;
+    if (used == kFlagSlots) return nullptr;
+    owner[used].dev = dev;
+    owner[used].st = st;
+    return base[dev] + used++;
 }
 
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,

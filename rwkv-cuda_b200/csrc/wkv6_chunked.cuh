@@ -21,6 +21,6 @@ int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, con
 // With a static decay (w_mode 2, 3) gw is summed over time into (B,C) instead of written per token.
 
 // one slot of a ring of device flags for `unsafe` (clear it in the stream before the forward)
-int* wkv6_chunked_next_flag();
+int* wkv6_chunked_flag(cudaStream_t st);
 
 }  // namespace rwkvb200

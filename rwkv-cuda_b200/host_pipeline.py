@@ -67,4 +67,11 @@ class Wkv7HostPipeline:
         return done
 
     def synchronize(self):
+        """Waits for the last forward_backward and checks the device status word: a bounded wait that
+        ran out inside a kernel leaves invalid results, which must not pass silently."""
         self.d2h.synchronize()
+        from . import _lib
+        st = _lib.lib().rwkvb200_device_status()
+        if st != 0:
+            raise _lib.RwkvB200Error(f"device status {st}: a bounded wait ran out inside a tensor-core kernel; results are invalid "
+                                     "(rwkvb200_device_status_clear resets the word)")
