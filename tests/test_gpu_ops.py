@@ -395,8 +395,7 @@ def test_wkv7_chunk_len_other_than_16(R):
 
 
 def test_wkv7_state_passing_composes(R):
-    """Two segments with the state handed over reproduce one pass over the whole sequence
-    (exactly for the state recurrence in fp32, y to bf16 rounding)."""
+    """Two segments with the state handed over reproduce one pass over the whole sequence."""
     B, T, H, N = 2, 128, 2, 64
     inp = Hh.v7_inputs(B, T, H, N, seed=11)
     d = {n: inp[n].to(torch.bfloat16).to(DEV).view(B, T, H, N).contiguous() for n in ("r", "w", "k", "v", "a", "b")}
@@ -410,15 +409,22 @@ def test_wkv7_state_passing_composes(R):
         return y, sT
 
     y, sT = fwd(0, T, s0)
-    ya, sm = fwd(0, 48, s0)
-    yb, sT2 = fwd(48, T, sm)
+    # a cut on a 32-token boundary keeps the kernels' chunks where they are: bit-identical
+    ya, sm = fwd(0, 64, s0)
+    yb, sT2 = fwd(64, T, sm)
     assert torch.equal(torch.cat([ya, yb], 1), y)
     assert torch.equal(sT2, sT)
+    # any other multiple of 16 regroups the tokens into different chunks: equal to rounding
+    ya, sm = fwd(0, 48, s0)
+    yb, sT3 = fwd(48, T, sm)
+    assert O.err_ratio(y.double().cpu(), torch.cat([ya, yb], 1).double().cpu()) < 4e-3   # two bf16 roundings
+    assert O.err_ratio(sT.double().cpu(), sT3.double().cpu()) < 1e-3
 
 
 def test_wkv6_chunked_calls_on_two_streams(R):
     """Two chunked RWKV-6 calls in flight on different streams, one of them with decays that force
-    the fall-back: each call has its own device flag, so neither disturbs the other."""
+    the fall-back: each stream has its own device flag, so neither disturbs the other -- however many
+    calls are queued (100 per stream here, more than any fixed ring of flags would hold)."""
     B, T, H, N = 2, 128, 2, 64
     dtype = torch.bfloat16
     C = H * N
@@ -433,7 +439,7 @@ def test_wkv6_chunked_calls_on_two_streams(R):
         cases[idx] = (O.wkv6(*xs, H), [x.to(dtype).to(DEV).contiguous() for x in (r, k, v)],
                       (-torch.exp(w_raw.to(dtype).float())).to(DEV).contiguous(), u.to(dtype).to(DEV).contiguous())
     torch.cuda.synchronize()
-    for rep in range(3):
+    for rep in range(100):
         for idx, st in enumerate(streams):
             _, (rd, kd, vd), ew, ud = cases[idx]
             with torch.cuda.stream(st):
