@@ -204,6 +204,15 @@ int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int chunk_len,
                            const float* sa, float* ds0, void* dr, void* dw, void* dk, void* dv,
                            void* da, void* db, void* stream);
 
+/* Inference-shaped RWKV-7 entry point: advances `state` (B,H,N,N) fp32, indexed [value i][key j] as the
+ * reference's s0 / sT (rwkv7_fast_fused/cuda/rwkv7_statepassing_clampw.cu:26-32, 78-80), by T >= 1 tokens
+ * IN PLACE and writes y (B,T,H,N).  Nothing is saved for a backward pass and T needs no alignment: T = 1
+ * is one decoding step, a long T a prompt.  The reference has no such launcher (its forward always saves
+ * s / sa and wants T % 16 == 0); same arithmetic as rwkvb200_wkv7_forward with s0 = sT = state. */
+int rwkvb200_wkv7_state_update(int dtype, int B, int T, int H, int N, float* state, const void* r,
+                               const void* w, const void* k, const void* v, const void* a, const void* b,
+                               void* y, void* stream);
+
 /* Kernel choice for RWKV-7 (process-wide; set it before launching work, not concurrently with it):
  * 0 = automatic (tensor-core kernels for bf16, N=64, chunk_len=16; general-shape kernels otherwise),
  * 1 = general-shape kernels only, 2 = tensor-core kernels or RWKVB200_EUNSUPPORTED.

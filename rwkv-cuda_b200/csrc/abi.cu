@@ -141,3 +141,19 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
     return wkv7_generic_backward(dtype, B, T, H, N, chunk_len, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv,
                                  da, db, as_stream(stream));
 }
+
+// Inference-shaped entry: advance the recurrent state by T >= 1 tokens in place and return y; nothing is
+// saved for a backward pass and T needs no alignment (T = 1 is one decoding step).
+extern "C" int rwkvb200_wkv7_state_update(int dtype, int B, int T, int H, int N, float* state, const void* r,
+                                          const void* w, const void* k, const void* v, const void* a, const void* b,
+                                          void* y, void* stream) {
+    if (int e = wkv7_check("wkv7_state_update", dtype, B, T, H, N, 1)) return e;
+    RWKV_NOTNULL(state); RWKV_NOTNULL(r); RWKV_NOTNULL(w); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(a); RWKV_NOTNULL(b);
+    RWKV_NOTNULL(y);
+    // long aligned prompts in bf16 with head size 64 take the tensor-core forward, everything else
+    // (decoding steps, odd lengths, other head sizes, fp32) the general-shape kernel
+    const bool tensor = g_wkv7_path.load() != 1 && dtype == RWKVB200_BF16 && N == 64 && T % 16 == 0 && T >= 64 &&
+                        aligned16({state, r, w, k, v, a, b, y});
+    if (tensor) return wkv7_l32_forward(B, T, H, state, r, w, k, v, a, b, y, state, nullptr, 0, as_stream(stream));
+    return wkv7_generic_forward(dtype, B, T, H, N, T, state, r, w, k, v, a, b, y, state, nullptr, nullptr, as_stream(stream));
+}

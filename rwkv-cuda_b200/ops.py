@@ -262,6 +262,15 @@ def wkv7_forward(s0, r, w, k, v, a, b, y, sT, s, sa):
              _stream(r))
 
 
+def wkv7_state_update(state, r, w, k, v, a, b, y):
+    """Inference: advance `state` (B,H,N,N fp32) in place by the T tokens of r..b (B,T,H,N) and write y."""
+    B, T, H, N = r.shape
+    d, f = r.dtype, torch.float32
+    with _dev(r, "r"):
+        call("rwkvb200_wkv7_state_update", _dt(r, "r"), B, T, H, N, _ptr(state, "state", f),
+             *_ptrs(d, r=r, w=w, k=k, v=v, a=a, b=b, y=y), _stream(r))
+
+
 def wkv7_backward(r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db):
     B, T, H, N, chunk = _v7_dims(r, s)
     d, f = r.dtype, torch.float32

@@ -224,4 +224,7 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("RWKV_CUDA_REF")
+    if not ref:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/RWKV-CUDA   (or RWKV_CUDA_REF=...)")
+    main(ref)

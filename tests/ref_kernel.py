@@ -48,6 +48,29 @@ def backward(r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db):
                                                                    dv, da, db)))
 
 
+_other = {}
+
+
+def other_lib(name):
+    """oracle/_ref/lib<name>_ref.so (rwkv5, rwkv6state) or None when it was not built."""
+    if name not in _other:
+        path = os.path.join(ROOT, "oracle", "_ref", f"lib{name}_ref.so")
+        _other[name] = ctypes.CDLL(path) if os.path.exists(path) else None
+        L = _other[name]
+        if L is not None:
+            vp, i = ctypes.c_void_p, ctypes.c_int
+            if name == "rwkv5":
+                L.ref_wkv5_forward.argtypes = [i] * 4 + [vp] * 6
+                L.ref_wkv5_backward.argtypes = [i] * 4 + [vp] * 12
+                L.ref_wkv5_forward.restype = L.ref_wkv5_backward.restype = None
+            else:
+                L.ref_wkv6state_forward.argtypes = [i] * 4 + [vp] * 7
+                L.ref_wkv6state_backward.argtypes = [i] * 4 + [vp] * 13
+                L.ref_wkv6state_forward.restype = L.ref_wkv6state_backward.restype = None
+                L.ref_wkv6state_T.restype = i
+    return _other[name]
+
+
 def run(inp, H, fwd, bwd):
     """inp: dict of CPU fp32 tensors (tests.helpers.v7_inputs).  Returns outputs as a dict."""
     dev = "cuda"

@@ -449,3 +449,28 @@ def test_wkv6_chunked_calls_on_two_streams(R):
     torch.cuda.synchronize()
     for idx in cases:
         Hh.assert_close(results[idx], cases[idx][0], Hh.tol_for(dtype), f"wkv6 stream {idx}")
+
+
+@pytest.mark.parametrize("dtype,N", [(torch.bfloat16, 64), (torch.float32, 64), (torch.bfloat16, 32)])
+def test_wkv7_state_update_decoding_and_prompt(R, dtype, N):
+    """Inference entry point: a prompt (any length) followed by single-token steps, state updated in place,
+    equals the fp64 formula on the concatenated sequence."""
+    B, H = 2, 3
+    lens = [96, 5, 1, 1, 1]
+    T = sum(lens)
+    inp = Hh.v7_inputs(B, T, H, N, seed=9)
+    x64 = {n: inp[n].to(dtype).double() for n in ("r", "w", "k", "v", "a", "b")}
+    y64, sT64 = O.wkv7(*(x64[n] for n in ("r", "w", "k", "v", "a", "b")), H, s0=inp["s0"].double())
+    d = {n: inp[n].to(dtype).to(DEV).view(B, T, H, N).contiguous() for n in ("r", "w", "k", "v", "a", "b")}
+    state = inp["s0"].to(DEV).clone()
+    ys, lo = [], 0
+    for L in lens:
+        seg = {n: x[:, lo:lo + L].contiguous() for n, x in d.items()}
+        y = sentinel(B, L, H, N, dtype=dtype)
+        R.ops.wkv7_state_update(state, seg["r"], seg["w"], seg["k"], seg["v"], seg["a"], seg["b"], y)
+        ys.append(y)
+        lo += L
+    torch.cuda.synchronize()
+    tol = Hh.tol_for(dtype)
+    Hh.assert_close(torch.cat(ys, 1).view(B, T, H * N), y64, tol, "y")
+    Hh.assert_close(state, sT64, tol, "state")

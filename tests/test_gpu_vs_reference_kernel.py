@@ -36,3 +36,87 @@ def test_error_no_worse_than_reference_kernel(B, T, H):
         if n not in ("sT", "ds0"):
             assert eo <= er * SLACK + 1e-6, f"{n}: ours {eo:.3e} worse than the reference kernel {er:.3e}"
     print("\n".join(report))
+
+
+def _p(t):
+    return t.data_ptr()
+
+
+@pytest.mark.skipif(ref_kernel.other_lib("rwkv5") is None, reason="reference RWKV-5 kernel library was not built")
+def test_wkv5_error_no_worse_than_reference_kernel():
+    """RWKV-5 bf16, head size 64 (wkv5_bf16/cuda/wkv5_cuda_v1b.cu compiled for sm_100a) on benchmark-like data."""
+    import rwkv_cuda_b200 as R
+    L = ref_kernel.other_lib("rwkv5")
+    B, T, H, N = 2, 512, 4, 64
+    C, bf, dev = H * N, torch.bfloat16, "cuda"
+    g = Hh.gen(42)
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.rand(g, H, N, lo=-6, hi=-1), Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(bf).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv5(*xs, H)
+    yo.backward(gy.to(bf).double())
+    want = dict(zip(("y", "gr", "gk", "gv", "gw", "gu"), [yo.detach()] + [x.grad for x in xs]))
+    rd, kd, vd, ud, gd = (x.to(bf).to(dev).contiguous() for x in (r, k, v, u, gy))
+    ew = -torch.exp(w_raw.to(bf).float()).to(dev)      # wkv5_bf16/run.py:63-64
+    eew = torch.exp(ew).contiguous()
+    res = {}
+    for who in ("ours", "reference"):
+        y, gr, gk, gv = (torch.empty(B, T, C, dtype=bf, device=dev) for _ in range(4))
+        gw, gu = torch.empty(B, C, dtype=bf, device=dev), torch.empty(B, C, dtype=bf, device=dev)
+        if who == "ours":
+            R.ops.wkv5_forward(B, T, C, H, rd, kd, vd, eew, ud, y)
+            R.ops.wkv5_backward(B, T, C, H, rd, kd, vd, eew, ew, ud, gd, gr, gk, gv, gw, gu)
+        else:
+            torch.cuda.synchronize()
+            L.ref_wkv5_forward(B, T, C, H, _p(rd), _p(kd), _p(vd), _p(eew), _p(ud), _p(y))
+            L.ref_wkv5_backward(B, T, C, H, _p(rd), _p(kd), _p(vd), _p(eew), _p(ew), _p(ud), _p(gd), _p(gr), _p(gk), _p(gv), _p(gw), _p(gu))
+        torch.cuda.synchronize()
+        res[who] = dict(y=y, gr=gr, gk=gk, gv=gv, gw=gw.float().sum(0).view(H, N), gu=gu.float().sum(0).view(H, N))
+    report = []
+    for n in ("y", "gr", "gk", "gv", "gw", "gu"):
+        eo = O.err_ratio(want[n], res["ours"][n].double().cpu().reshape(want[n].shape))
+        er = O.err_ratio(want[n], res["reference"][n].double().cpu().reshape(want[n].shape))
+        report.append(f"{n}: ours {eo:.3e} reference kernel {er:.3e}")
+        assert eo <= Hh.TOL_BF16, f"{n}: {eo:.3e} > 2e-2"
+        assert eo <= er * SLACK + 1e-6, f"{n}: ours {eo:.3e} worse than the reference kernel {er:.3e}"
+    print("\n".join(report))
+
+
+@pytest.mark.skipif(ref_kernel.other_lib("rwkv6state") is None, reason="reference RWKV-6 state kernel library was not built")
+def test_wkv6state_error_no_worse_than_reference_kernel():
+    """RWKV-6 with an initial state, everything bf16 as in the reference operator (wkv6_state/cuda/
+    wkv6state_cuda_v1a.cu compiled for sm_100a with its sequence length baked in)."""
+    import rwkv_cuda_b200 as R
+    L = ref_kernel.other_lib("rwkv6state")
+    B, T, H, N = 2, L.ref_wkv6state_T(), 4, 64
+    C, bf, dev = H * N, torch.bfloat16, "cuda"
+    g = Hh.gen(42)
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.randn(g, B, T, C) - 5.0, Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    s = 0.1 * Hh.randn(g, B, H, N, N)
+    xs = [x.to(bf).double().requires_grad_(True) for x in (r, k, v, w_raw, u, s)]
+    yo = O.wkv6(*xs[:5], H, s0=xs[5])
+    yo.backward(gy.to(bf).double())
+    want = dict(zip(("y", "gr", "gk", "gv", "gw", "gu", "gs"), [yo.detach()] + [x.grad for x in xs]))
+    rd, kd, vd, wd, ud, sd, gd = (x.to(bf).to(dev).contiguous() for x in (r, k, v, w_raw, u, s, gy))
+    res = {}
+    for who in ("ours", "reference"):
+        y, gr, gk, gv, gw = (torch.zeros(B, T, C, dtype=bf, device=dev) for _ in range(5))
+        gu, gs = torch.zeros(B, C, dtype=bf, device=dev), torch.zeros(B, H, N, N, dtype=bf, device=dev)
+        if who == "ours":
+            R.ops.wkv6state_forward(B, T, C, H, rd, kd, vd, wd, ud, sd, y)
+            R.ops.wkv6state_backward(B, T, C, H, rd, kd, vd, wd, ud, sd, gd, gr, gk, gv, gw, gu, gs)
+        else:
+            torch.cuda.synchronize()
+            L.ref_wkv6state_forward(B, T, C, H, _p(rd), _p(kd), _p(vd), _p(wd), _p(ud), _p(sd), _p(y))
+            L.ref_wkv6state_backward(B, T, C, H, _p(rd), _p(kd), _p(vd), _p(wd), _p(ud), _p(sd), _p(gd), _p(gr), _p(gk), _p(gv), _p(gw), _p(gu), _p(gs))
+        torch.cuda.synchronize()
+        res[who] = dict(y=y, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu.float().sum(0).view(H, N), gs=gs)
+    report = []
+    for n in ("y", "gr", "gk", "gv", "gw", "gu", "gs"):
+        eo = O.err_ratio(want[n], res["ours"][n].double().cpu().reshape(want[n].shape))
+        er = O.err_ratio(want[n], res["reference"][n].double().cpu().reshape(want[n].shape))
+        report.append(f"{n}: ours {eo:.3e} reference kernel {er:.3e}")
+        assert eo <= Hh.TOL_BF16, f"{n}: {eo:.3e} > 2e-2"
+        assert eo <= er * SLACK + 1e-6, f"{n}: ours {eo:.3e} worse than the reference kernel {er:.3e}"
+    print("\n".join(report))
