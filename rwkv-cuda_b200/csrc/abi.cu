@@ -50,6 +50,24 @@ extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 // must see the same value (the saved buffers differ between the two kernel families).
 static std::atomic<int> g_wkv7_path{0};
 static std::atomic<int> g_wkv7_test_expire{0};
+static std::atomic<int> g_wkv7_bwd_form{0};   // 0 automatic, 1 one-group backward, 2 two-stage backward
+
+static int sm_count() {
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> cache[kMaxDevices] = {};
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    if ((n = cache[dev].load()) != 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cache[dev].store(n);
+    return n;
+}
+
+extern "C" int rwkvb200_wkv7_select_backward_form(int form) {
+    RWKV_REQUIRE(form >= 0 && form <= 2, RWKVB200_EINVAL, "wkv7_select_backward_form: form %d not in 0..2", form);
+    g_wkv7_bwd_form.store(form);
+    return RWKVB200_OK;
+}
 
 extern "C" int rwkvb200_wkv7_select_path(int path) {
     RWKV_REQUIRE(path >= 0 && path <= 2, RWKVB200_EINVAL, "wkv7_select_path: path %d not in 0..2", path);
@@ -96,12 +114,18 @@ extern "C" int rwkvb200_device_status(void) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
+    const int p = wkv7_l32_bwdp_error(0);
+    if (p < 0) {
+        set_error("device_status: reading the status words failed");
+        return RWKVB200_ECUDA;
+    }
     if (f) return 10 + f;
-    return g ? 20 + g : 0;
+    if (g) return 20 + g;
+    return p;   // the two-stage backward records 30.. (front group) or 40.. (back group)
 }
 
 extern "C" int rwkvb200_device_status_clear(void) {
-    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
+    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
     return RWKVB200_OK;
 }
 
@@ -136,6 +160,12 @@ extern "C" int rwkvb200_wkv7_backward(int dtype, int B, int T, int H, int N, int
     if (tensor) {
         RWKV_REQUIRE(aligned16({r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv, da, db}), RWKVB200_EALIGN,
                      "wkv7_backward: the bf16 N=64 path needs 16-byte aligned tensors");
+        // at most one unit per SM: the time is one unit's chain of chunks, which the two-stage form (one thread
+        // block per SM, two warp groups on consecutive chunks) nearly halves; with more units per SM two
+        // independent one-group blocks per SM give more throughput
+        const int form = g_wkv7_bwd_form.load();
+        if (form == 2 || (form == 0 && (long long)B * H <= sm_count()))
+            return wkv7_l32_backward_pipelined(B, T, H, r, w, k, v, a, b, dy, dsT, s, ds0, dr, dw, dk, dv, da, db, as_stream(stream));
         return wkv7_l32_backward(B, T, H, r, w, k, v, a, b, dy, dsT, s, ds0, dr, dw, dk, dv, da, db, as_stream(stream));
     }
     return wkv7_generic_backward(dtype, B, T, H, N, chunk_len, r, w, k, v, a, b, dy, dsT, s, sa, ds0, dr, dw, dk, dv,

@@ -22,6 +22,12 @@ int wkv7_l32_forward(int B, int T, int H, const float* s0, const void* r, const 
 int wkv7_l32_backward(int B, int T, int H, const void* r, const void* w, const void* k, const void* v, const void* a,
                       const void* b, const void* dy, const float* dsT, const float* s, float* ds0, void* dr, void* dw,
                       void* dk, void* dv, void* da, void* db, cudaStream_t st);
+// The backward as two warp groups working on consecutive chunks (one thread block per SM; same
+// products, results equal to rounding); for launches with at most one unit per SM.  Error word: read (clear = 0) or reset (clear = 1).
+int wkv7_l32_backward_pipelined(int B, int T, int H, const void* r, const void* w, const void* k, const void* v, const void* a,
+                                const void* b, const void* dy, const float* dsT, const float* s, float* ds0, void* dr, void* dw,
+                                void* dk, void* dv, void* da, void* db, cudaStream_t st);
+int wkv7_l32_bwdp_error(int clear);
 // sticky per-device status words of the two kernels (0 = fine) and their reset
 int wkv7_l32_fwd_error();
 int wkv7_l32_bwd_error();

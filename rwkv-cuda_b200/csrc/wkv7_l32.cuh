@@ -147,6 +147,12 @@ struct ChainSync {
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar))); }
 
+// barrier among `nthreads` threads: the whole CTA (id 0) or a named barrier of a warp group
+__device__ __forceinline__ void group_sync(int id, int nthreads) {
+    if (id == 0) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // ---- the part of a chunk that does not depend on the carried state ---------------------------------
 // Raw inputs of one chunk as loaded by a thread: channels (2*lane, 2*lane+1) of TPW consecutive tokens
 // (token index inside the chunk = TPW*warp + q).  NX tensors: r w k v a b [dy].
@@ -174,11 +180,12 @@ __device__ __forceinline__ void fetch_chunk(RawChunk<NX, TPW>& rc, const bf16* c
 //   V rows = v_t (dst_v, a 32-row half-array pair at the given half stride), optionally dY the same way,
 //   We[j] = decay over the whole chunk, and optionally the cumulative log2-decays lam[t][j] (plain [32][LAMP]).
 // Tokens at or beyond `valid` (counted inside the chunk) are neutral: no decay, zero vectors.
-// Hs is a [NW][64] exchange buffer.  Contains one CTA-wide barrier; the caller synchronises afterwards.
+// Hs is a [NW][64] exchange buffer.  Contains one barrier among the NW calling warps (the CTA, or the named
+// barrier `bar_id` of a warp group); the caller synchronises afterwards.
 template <int NX, int TPW, int NW>
 __device__ __forceinline__ void prepare_operands(const RawChunk<NX, TPW>& rc, int valid, unsigned char* AR, unsigned char* BK,
                                                  unsigned char* dstV, int halfV, unsigned char* dstDY, int halfDY,
-                                                 float* We, float* Hs, float* lam_out, int warp, int lane) {
+                                                 float* We, float* Hs, float* lam_out, int warp, int lane, int bar_id = 0) {
     const int j0 = 2 * lane, t0 = TPW * warp;
     float cs[TPW][2];
     float run0 = 0.f, run1 = 0.f;
@@ -192,7 +199,7 @@ __device__ __forceinline__ void prepare_operands(const RawChunk<NX, TPW>& rc, in
         cs[q][0] = run0; cs[q][1] = run1;
     }
     *reinterpret_cast<float2*>(Hs + warp * 64 + j0) = make_float2(run0, run1);
-    __syncthreads();
+    group_sync(bar_id, NW * 32);
     float base0 = 0.f, base1 = 0.f, tot0 = 0.f, tot1 = 0.f;
 #pragma unroll
     for (int gq = 0; gq < NW; ++gq) {
