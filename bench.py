@@ -106,7 +106,7 @@ class V7Workload:
     # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel per token, from the ncu
     # capture of the reduced case (profiles/wkv7_tcgen05_chunk32_B8_T1024.md); traffic is
     # proportional to the token count
-    dram_bytes_per_token_bwd = (0.746658e9 + 0.376867e9) / (8 * 1024)
+    dram_bytes_per_token_bwd = (0.746671e9 + 0.377635e9) / (8 * 1024)
 
     def e2e_step(self):
         """Host buffers in, host buffers out, through the public host-buffer API
@@ -384,6 +384,68 @@ def run_secondary(op, args):
     print(json.dumps(out), flush=True)
 
 
+def run_wkv5_sharded(args, rank, world, local):
+    """BASELINE configuration 3 (RWKV-5 bf16 B8 T4096 C4096 N64) sharded by batch over the ranks, with the one
+    collective this library has: gw and gu are reduced over the local batch in fp32 into one buffer
+    (rwkvb200_reduce_batch_partials) and that buffer is all-reduced once over NCCL, on a side stream.
+    Every rank draws the same seed-42 batch and keeps its rows.  Rank 0 prints one JSON line."""
+    import torch.distributed as dist
+    import rwkv_cuda_b200 as R
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    B, T, H, N = args.batch or 8, args.seq or 4096, 64, 64
+    C, bf = H * N, torch.bfloat16
+    assert B % world == 0
+    bl, lo = B // world, rank * (B // world)
+    g = torch.Generator(device=dev)
+    g.manual_seed(42)
+    full = lambda sc=1.0: torch.randn(B, T, C, generator=g, device=dev) * sc
+    r, k, v = (full(0.5)[lo:lo + bl].to(bf).contiguous() for _ in range(3))
+    gy = full()[lo:lo + bl].to(bf).contiguous()
+    wraw = (torch.rand(H, N, generator=g, device=dev) * 5 - 6).to(bf)
+    u = (torch.rand(H, N, generator=g, device=dev) * 2 - 1).to(bf)
+    ew = -torch.exp(wraw.float())
+    eew = torch.exp(ew)
+    y, gr, gk, gv = (torch.empty(bl, T, C, dtype=bf, device=dev) for _ in range(4))
+    gw, gu = torch.empty(bl, C, dtype=bf, device=dev), torch.empty(bl, C, dtype=bf, device=dev)
+    red = R.dist.ParamGradReducer(dev, 2 * C)
+
+    def step():
+        R.ops.wkv5_forward(bl, T, C, H, r, k, v, eew, u, y)
+        R.ops.wkv5_backward(bl, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu)
+        red.reset()
+        red.add(gw); red.add(gu)
+        red.launch()
+        return red.result(0), red.result(1)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        gws, gus = step()
+    e1.record()
+    dist.barrier(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # the same reduction on one rank over the whole batch would be sum over all rows: check the collective
+    chk = torch.stack([gws.sum(), gus.sum()]).double()
+    loc = torch.stack([gw.float().sum(), gu.float().sum()]).double()
+    dist.all_reduce(loc, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        ms = t.item() / args.steps
+        print(json.dumps({"metric": "WKV fwd+bwd tokens/s, RWKV-5 B8 T4096 C4096 bf16 (batch-sharded, parameter gradients all-reduced)",
+                          "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"wkv5 fwd+bwd bf16 B{B} T{T} C{C} N{N}", "batch_per_gpu": bl,
+                                     "parallelism": f"batch-sharded x{world}; one fp32 all-reduce of {2 * C} floats (NCCL) per step on a side stream"},
+                          "collective_check": {"allreduced_sum": chk.tolist(), "sum_of_local_sums": loc.tolist(),
+                                               "rel_diff": ((chk - loc).abs() / loc.abs().clamp_min(1e-30)).tolist()}}), flush=True)
+    dist.destroy_process_group()
+
+
 def reference_kernel_timing(wl, fwd_ms, bwd_ms):
     """The reference project's own CUDA kernel (built as a test-only checker into oracle/_ref/ where a
     reference checkout was present) on this rank's device tensors, outside the timed region: its times,
@@ -456,6 +518,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
+    if args.op == "wkv5" and world > 1:
+        run_wkv5_sharded(args, rank, world, local)
+        return
     if args.op != "wkv7":
         if rank == 0:
             run_secondary(args.op, args)

@@ -92,6 +92,12 @@ int rwkvb200_wkv5_backward(int dtype, int B, int T, int C, int H, const void* r,
                            const void* v, const float* w, const float* ww, const void* u,
                            const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
                            void* stream);
+/* Sum of the per-batch parameter-gradient partials the backward kernels emit, gw / gu (B,n) in `dtype`,
+ * into fp32 out[n], accumulated in fp32 in batch order (deterministic).  Replaces the harnesses'
+ * `torch.sum(gw, 0)` on bf16 partials (wkv5_bf16/run.py:86-87, wkv6/run.py:169, wkv/run.py:115-116), whose
+ * result is rounded to bf16; several partials can be reduced into one fp32 buffer, which is then what a
+ * multi-GPU run all-reduces once. */
+int rwkvb200_reduce_batch_partials(int dtype, int B, int n, const void* partial, float* out, void* stream);
 /* The same backward with a caller-provided work buffer of rwkvb200_wkv5_scratch_bytes(B,T,C) bytes
  * (16 per element; contents undefined afterwards).  No counterpart in the reference.  With it,
  * bf16 / head size 64 / T a multiple of 16 runs on the chunked tensor-core kernels (RWKV-5 is

@@ -369,3 +369,30 @@ extern "C" int rwkvb200_wkv5a_backward(int dtype, int B, int T, int C, int H, co
                : launch_bwd<bf16, true>(B, T, C, H, r, k, v, w1, ww1, u1, w2, ww2, u2, gy, gr, gk, gv, gw1, gu1,
                                         gw2, gu2, as_stream(stream));
 }
+
+// ---- parameter gradients: per-batch partials -> one fp32 vector ------------------------------------------
+namespace rwkvb200 {
+namespace {
+// out[off + j] = sum_b partial[b][j], fp32 accumulation in batch order (deterministic); one thread per column
+template <typename E>
+__global__ void reduce_batch_partials_kernel(int B, int n, const E* __restrict__ partial, float* __restrict__ out) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    float acc = 0.f;
+    for (int b = 0; b < B; ++b) acc += to_f(partial[(i64)b * n + j]);
+    out[j] = acc;
+}
+}  // namespace
+}  // namespace rwkvb200
+
+extern "C" int rwkvb200_reduce_batch_partials(int dtype, int B, int n, const void* partial, float* out, void* stream) {
+    RWKV_REQUIRE(dtype == RWKVB200_F32 || dtype == RWKVB200_BF16, RWKVB200_EINVAL, "reduce_batch_partials: unknown dtype %d", dtype);
+    RWKV_REQUIRE(B > 0 && n > 0, RWKVB200_EINVAL, "reduce_batch_partials: B=%d n=%d must be positive", B, n);
+    RWKV_NOTNULL(partial); RWKV_NOTNULL(out);
+    const int threads = 128, blocks = (n + threads - 1) / threads;
+    if (dtype == RWKVB200_F32)
+        reduce_batch_partials_kernel<float><<<blocks, threads, 0, as_stream(stream)>>>(B, n, (const float*)partial, out);
+    else
+        reduce_batch_partials_kernel<bf16><<<blocks, threads, 0, as_stream(stream)>>>(B, n, (const bf16*)partial, out);
+    return check_launch("reduce_batch_partials");
+}

@@ -54,3 +54,49 @@ def allreduce_param_grads(grads, group=None, async_op=False):
         return finish
     finish()
     return None
+
+
+class ParamGradReducer:
+    """Parameter gradients of one backward call, summed over the local batch and over the ranks.
+
+    `add(partial)` reduces a per-batch partial (B, n) -- what the backward kernels emit -- over the batch
+    in fp32 into the next slice of ONE fp32 buffer (no bf16 round trip), on the caller's stream;
+    `launch()` enqueues the all-reduce of that buffer on a side stream as soon as the reductions are
+    done, so it overlaps whatever the caller enqueues next; `result(i)` waits for it and returns the
+    i-th reduced gradient as a view of the buffer.  Without a process group it is the local sum."""
+
+    def __init__(self, device, capacity, group=None):
+        self.buf = torch.zeros(capacity, dtype=torch.float32, device=device)
+        self.side = torch.cuda.Stream(device)
+        self.group, self.spans, self.off, self.work, self.done = group, [], 0, None, None
+
+    def add(self, partial):
+        from . import ops
+        n = partial.numel() // partial.shape[0]
+        if self.off + n > self.buf.numel():
+            raise ValueError("ParamGradReducer: capacity exceeded")
+        ops.reduce_batch_partials(partial, self.buf[self.off:self.off + n])
+        self.spans.append((self.off, n))
+        self.off += n
+        return len(self.spans) - 1
+
+    def launch(self):
+        cur = torch.cuda.current_stream(self.buf.device)
+        self.side.wait_stream(cur)
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            with torch.cuda.stream(self.side):
+                self.work = dist.all_reduce(self.buf[:self.off], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self.done = self.side.record_event() if self.work is None else None
+
+    def result(self, i):
+        cur = torch.cuda.current_stream(self.buf.device)
+        if self.work is not None:
+            self.work.wait()          # makes the current stream wait for the collective
+            self.work = None
+        elif self.done is not None:
+            cur.wait_event(self.done)
+        lo, n = self.spans[i]
+        return self.buf[lo:lo + n]
+
+    def reset(self):
+        self.spans, self.off, self.work, self.done = [], 0, None, None

@@ -134,6 +134,16 @@ def wkv5_backward(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu):
              *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), sc.data_ptr(), _stream(r))
 
 
+def reduce_batch_partials(partial, out):
+    """out (n,) fp32 <- sum over dim 0 of partial (B, n) (bf16 or fp32), accumulated in fp32."""
+    B = partial.shape[0]
+    n = partial.numel() // B
+    _numel(out, n, "out")
+    with _dev(partial, "partial"):
+        call("rwkvb200_reduce_batch_partials", _dt(partial, "partial"), B, n, _ptr(partial, "partial", partial.dtype),
+             _ptr(out, "out", torch.float32), _stream(partial))
+
+
 # ---- RWKV-5a (wkv5a/cuda/wkv5a_op.cpp:9-17) -------------------------------------------
 def wkv5a_forward(B, T, C, H, r, k, v, w1, u1, w2, u2, y):
     d, f = r.dtype, torch.float32
