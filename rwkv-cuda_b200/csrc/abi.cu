@@ -50,7 +50,7 @@ extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 // must see the same value (the saved buffers differ between the two kernel families).
 static std::atomic<int> g_wkv7_path{0};
 static std::atomic<int> g_wkv7_test_expire{0};
-static std::atomic<int> g_wkv7_bwd_form{0};   // 0 automatic, 1 one-group backward, 2 two-stage backward
+static std::atomic<int> g_wkv7_bwd_form{0};   // 0 automatic, 1 one-group kernels, 2 two-stage kernels
 
 static int sm_count() {
     constexpr int kMaxDevices = 64;
@@ -63,8 +63,8 @@ static int sm_count() {
     return n;
 }
 
-extern "C" int rwkvb200_wkv7_select_backward_form(int form) {
-    RWKV_REQUIRE(form >= 0 && form <= 2, RWKVB200_EINVAL, "wkv7_select_backward_form: form %d not in 0..2", form);
+extern "C" int rwkvb200_wkv7_select_form(int form) {
+    RWKV_REQUIRE(form >= 0 && form <= 2, RWKVB200_EINVAL, "wkv7_select_form: form %d not in 0..2", form);
     g_wkv7_bwd_form.store(form);
     return RWKVB200_OK;
 }
@@ -114,18 +114,19 @@ extern "C" int rwkvb200_device_status(void) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
-    const int p = wkv7_l32_bwdp_error(0);
-    if (p < 0) {
+    const int p = wkv7_l32_bwdp_error(0), q = wkv7_l32_fwdp_error(0);
+    if (p < 0 || q < 0) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
     if (f) return 10 + f;
     if (g) return 20 + g;
-    return p;   // the two-stage backward records 30.. (front group) or 40.. (back group)
+    if (p) return p;            // the two-stage backward records 30.. (front group) or 40.. (back group)
+    return q ? q + 20 : 0;      // the two-stage forward 50.. / 60..
 }
 
 extern "C" int rwkvb200_device_status_clear(void) {
-    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
+    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0 && wkv7_l32_fwdp_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
     return RWKVB200_OK;
 }
 
@@ -142,7 +143,11 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
     if (tensor) {
         RWKV_REQUIRE(aligned16({s0, r, w, k, v, a, b, y, sT, s, sa}), RWKVB200_EALIGN,
                      "wkv7_forward: the bf16 N=64 path needs 16-byte aligned tensors");
-        return wkv7_l32_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, g_wkv7_test_expire.exchange(0), as_stream(stream));
+        const int form = g_wkv7_bwd_form.load(), expire = g_wkv7_test_expire.exchange(0);
+        // at most one unit per SM: the two-stage form (see the backward) shortens the chain of chunks
+        if (!expire && (form == 2 || (form == 0 && (long long)B * H <= sm_count())))
+            return wkv7_l32_forward_pipelined(B, T, H, s0, r, w, k, v, a, b, y, sT, s, as_stream(stream));
+        return wkv7_l32_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, expire, as_stream(stream));
     }
     return wkv7_generic_forward(dtype, B, T, H, N, chunk_len, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));
 }

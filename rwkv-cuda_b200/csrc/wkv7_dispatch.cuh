@@ -28,6 +28,10 @@ int wkv7_l32_backward_pipelined(int B, int T, int H, const void* r, const void* 
                                 const void* b, const void* dy, const float* dsT, const float* s, float* ds0, void* dr, void* dw,
                                 void* dk, void* dv, void* da, void* db, cudaStream_t st);
 int wkv7_l32_bwdp_error(int clear);
+// the forward in the same two-stage form (front: operands, U, inverses; back: the dependent chain, y, state)
+int wkv7_l32_forward_pipelined(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k, const void* v,
+                               const void* a, const void* b, void* y, float* sT, float* s, cudaStream_t st);
+int wkv7_l32_fwdp_error(int clear);
 // sticky per-device status words of the two kernels (0 = fine) and their reset
 int wkv7_l32_fwd_error();
 int wkv7_l32_bwd_error();
