@@ -1,16 +1,10 @@
-// Building blocks of the chunked (tensor-core) RWKV-7 kernels: head size 64, chunk of 16 tokens.
+// Building blocks shared by the chunked (tensor-core) kernels: TF32 rounding, single-instruction
+// approximations, bf16 pair conversion, cp.async, the optional phase counters (used by the RWKV-7
+// tcgen05 kernels and by the 16-token RWKV-6 / RWKV-5 kernels) and the mma.sync m16n8k8 TF32 products
+// with their fragment loaders (used by the RWKV-6 / RWKV-5 kernels, head size 64, chunks of 16 tokens).
 //
-// Chunked form of the recurrence.  S is [value i][key j]; within a chunk of L = 16 tokens let
-// W_t = prod_{tau<=t} d_tau (inclusive, per key channel), W_{-1} = 1, We = W_15, and
-//   a~_t = a_t*W_{t-1}   r~_t = r_t*W_t   b~_s = b_s/W_s   k~_s = k_s/W_s   b^_s = b~_s*We   k^_s = k~_s*We
-//   U_ab[s,t] = b~_s.a~_t (s<t)   U_ak[s,t] = k~_s.a~_t (s<t)   U_br[s,t] = b~_s.r~_t (s<=t)   U_kr[s,t] = k~_s.r~_t (s<=t)
-//   T = (I - U_ab)^-1
-// then with S0 the state at the start of the chunk, V = [v_t], SA = [sa_t], Y = [y_t] (64 x 16):
-//   SA = (S0 A~ + V U_ak) T          Y = S0 R~ + SA U_br + V U_kr          S_end = S0 diag(We) + SA B^ + V K^
-// The divisions by W are safe because the soft clamp keeps d >= 0.545, so W >= 0.545^16 = 6e-5.
-//
-// All contractions run on mma.sync m16n8k8 TF32 (operands rounded to TF32, fp32 accumulate);
-// the state itself, the decays, the triangular inverse and every elementwise step stay fp32.
+// All contractions take operands rounded to TF32 and accumulate in fp32; states, decays and every
+// elementwise step stay fp32.
 #pragma once
 #include "common.cuh"
 
@@ -32,7 +26,6 @@ constexpr float kWScale2 = kWScale * 1.4426950408889634f;   // the same in log2 
 // instructions.  The cvt form issues on the quarter-rate conversion pipe, which the four resident
 // CTAs of an SM hit at the same time during operand preparation.
 __device__ __forceinline__ uint32_t tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
-__device__ __forceinline__ float tf32f(float x) { return __uint_as_float(tf32(x)); }
 // The same rounding for a value that only ever feeds a tensor-core operand: the tensor core reads the
 // upper 19 bits of a TF32 operand register or shared-memory word and ignores the rest, so adding
 // half a unit of the last kept place is enough (one instruction; results are bit-identical to tf32()).
@@ -132,44 +125,6 @@ __device__ __forceinline__ void gemm_rs_plain(float (*acc)[4], const uint32_t (*
         }
 }
 
-// A fragments (KS k-steps) of rows row0+g / row0+g+8 from a row-major [m][k] array (pitch pa).
-template <int KS>
-__device__ __forceinline__ void load_a(uint32_t (*areg)[4], const float* am, int pa, int row0, int g, int t) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-        const uint2 lo = lds2(am + (row0 + g) * pa + ks * 8 + 2 * t);
-        const uint2 hi = lds2(am + (row0 + g + 8) * pa + ks * 8 + 2 * t);
-        areg[ks][0] = lo.x; areg[ks][1] = hi.x; areg[ks][2] = lo.y; areg[ks][3] = hi.y;
-    }
-}
-
-// Same product with B read from a row-major [k][n] array (pitch pb): element (k, n) at bm[k*pb + n].
-template <int NTILES, int KS>
-__device__ __forceinline__ void gemm_rs_kmaj(float (*acc)[4], const uint32_t (*areg)[4], const float* bm, int pb,
-                                             int g, int t) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks)
-#pragma unroll
-        for (int nt = 0; nt < NTILES; ++nt) {
-            const uint32_t b0 = __float_as_uint(bm[(ks * 8 + 2 * t) * pb + nt * 8 + g]);
-            const uint32_t b1 = __float_as_uint(bm[(ks * 8 + 2 * t + 1) * pb + nt * 8 + g]);
-            mma8(acc[nt], areg[ks][0], areg[ks][1], areg[ks][2], areg[ks][3], b0, b1);
-        }
-}
-
-// A fragments of rows row0+g / row0+g+8 from a row-major [k][m] array (pitch pa): element (m, k) at am[k*pa + m].
-template <int KS>
-__device__ __forceinline__ void load_a_kmaj(uint32_t (*areg)[4], const float* am, int pa, int row0, int g, int t) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-        const float* p0 = am + (ks * 8 + 2 * t) * pa + row0 + g;
-        areg[ks][0] = __float_as_uint(p0[0]);
-        areg[ks][1] = __float_as_uint(p0[8]);
-        areg[ks][2] = __float_as_uint(p0[pa]);
-        areg[ks][3] = __float_as_uint(p0[pa + 8]);
-    }
-}
-
 // A fragments from a row-major [m][k] array whose k positions are channel-permuted.
 template <int KS>
 __device__ __forceinline__ void load_a_plain(uint32_t (*areg)[4], const float* am, int pa, int row0, int g, int t) {
@@ -213,16 +168,6 @@ __device__ __forceinline__ void gemm_rs_kperm(float (*acc)[4], const uint32_t (*
         }
 }
 
-// accumulator tiles -> A fragments (rounded to TF32)
-template <int KS>
-__device__ __forceinline__ void acc_to_a(uint32_t (*areg)[4], const float (*acc)[4]) {
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-        areg[ks][0] = tf32r(acc[ks][0]); areg[ks][1] = tf32r(acc[ks][2]);
-        areg[ks][2] = tf32r(acc[ks][1]); areg[ks][3] = tf32r(acc[ks][3]);
-    }
-}
-
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
@@ -255,58 +200,6 @@ static __device__ unsigned long long g_phase_clocks[8][16];
 #define WKV7_PHASE(k)
 #define WKV7_PHASE_READER(name)
 #endif
-
-// T = (I - U)^-1 for a strictly upper triangular 16x16 U (U[s][m], pitch PU, 16-byte aligned rows,
-// fp32), by back substitution in fp32; lane t (< 16) owns column t:
-//   T[s,t] = [s == t] + sum_{m>s} U[s,m] T[m,t]      (rows s = 14 .. 0; zero below the diagonal by itself)
-// Software-pipelined: the sum of row s is split into its newest term (m = s+1), the second newest
-// (m = s+2) and the rest (m >= s+3); the rest of row s-1 is accumulated between the two final FMAs
-// of row s, so one FMA per row sits on the dependent chain, and rows are fetched (float4) three rows
-// ahead.  Measured alone on a B200: 530 cycles against 620 for the plain loop and 890 for a 2x2
-// blocked variant with a shared-memory exchange.  Result rounded to TF32 and stored transposed
-// (Tt[t][s]) or, with NATURAL, as T[s][t].  Called by one full warp.
-template <bool NATURAL = false>
-__device__ __forceinline__ void tri_inverse(const float* U, float* Tt, int lane) {
-    const int t = lane & 15;
-    float col[L], tp[L];
-    float4 rw[L][4];
-#pragma unroll
-    for (int s = 0; s < L; ++s) tp[s] = (s == t) ? 1.f : 0.f;
-    col[L - 1] = tp[L - 1];
-    auto load_row = [&](int s) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            if (4 * q + 3 >= s + 1) rw[s][q] = *reinterpret_cast<const float4*>(U + s * PU + 4 * q);
-    };
-    auto u = [&](int s, int m) {
-        const float4 rr = rw[s][m >> 2];
-        return (m & 3) == 0 ? rr.x : (m & 3) == 1 ? rr.y : (m & 3) == 2 ? rr.z : rr.w;
-    };
-    load_row(14); load_row(13); load_row(12);
-#pragma unroll
-    for (int s = L - 2; s >= 0; --s) {
-        if (s >= 3) load_row(s - 3);
-        float x = tp[s];
-        if (s + 2 < L) x = fmaf(u(s, s + 2), col[s + 2], x);
-        if (s >= 1) {   // rest of row s-1: m >= s+2, all of those columns are final
-            float a0 = tp[s - 1], a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-            for (int m = s + 2; m < L; ++m) {
-                const float uu = u(s - 1, m);
-                if ((m & 3) == 0) a0 = fmaf(uu, col[m], a0);
-                else if ((m & 3) == 1) a1 = fmaf(uu, col[m], a1);
-                else if ((m & 3) == 2) a2 = fmaf(uu, col[m], a2);
-                else a3 = fmaf(uu, col[m], a3);
-            }
-            tp[s - 1] = (a0 + a1) + (a2 + a3);
-        }
-        col[s] = fmaf(u(s, s + 1), col[s + 1], x);
-    }
-    if (lane < 16) {
-#pragma unroll
-        for (int s = 0; s < L; ++s) Tt[NATURAL ? s * PU + t : t * PU + s] = tf32rf(col[s]);
-    }
-}
 
 }  // namespace v7c
 }  // namespace rwkvb200

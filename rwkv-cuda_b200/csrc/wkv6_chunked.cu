@@ -6,7 +6,7 @@
 // state at the start of the chunk, V = [v_t], Y = [y_t] (64 x 16):
 //   A[s,t] = k~_s.r~_t (s < t),  A[t,t] = sum_j r_t[j] u[j] k_t[j]
 //   Y = S0 R~ + V A          S_end = (S0 + V K~) diag(We)
-// i.e. the RWKV-7 chunk (wkv7_chunked.cuh) without the a/b terms: no inverse, one 16x16 matrix.
+// i.e. the RWKV-7 chunk (chunk_tf32.cuh) without the a/b terms: no inverse, one 16x16 matrix.
 // One CTA of 4 warps per (batch, head); warp w owns state rows 16w..16w+15 as accumulator tiles
 // for the whole sequence.
 //
@@ -14,7 +14,7 @@
 // has no clamp on w.  The kernel therefore raises a flag when the summed log-decay of any channel
 // over a chunk exceeds 80 (P < 1.8e-35); the launcher then runs the general-shape kernel over the
 // same problem (it starts by reading the flag, and returns at once when the flag is clear).
-#include "wkv7_chunked.cuh"
+#include "chunk_tf32.cuh"
 #include "wkv6_chunked.cuh"
 #include <atomic>
 #include <mutex>

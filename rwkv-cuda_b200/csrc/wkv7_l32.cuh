@@ -267,8 +267,12 @@ __device__ __forceinline__ void scatter_u(const float (*u)[4], int quarter, int 
 // Inverse of a 16x16 unit upper triangular block: T = (I - U)^-1 for the strictly upper triangular 16x16
 // block that starts at Ub (plain fp32, pitch PITCH floats, rows 16-byte aligned); result rounded to TF32
 // into the diagonal block at (r0, r0) of the swizzled [32][32] operand array D0 (whose off-diagonal blocks
-// stay zero).  Back substitution, lane t (< 16) owns column t; software-pipelined as in
-// v7c::tri_inverse (one FMA per row on the dependent chain).  Called by one full warp.
+// stay zero).  Back substitution in fp32, lane t (< 16) owns column t:
+//   T[s,t] = [s == t] + sum_{m>s} U[s,m] T[m,t]      (rows s = 14 .. 0; zero below the diagonal by itself)
+// Software-pipelined: the sum of row s is split into its newest term (m = s+1), the second newest (m = s+2)
+// and the rest (m >= s+3); the rest of row s-1 is accumulated between the two final FMAs of row s, so one
+// FMA per row sits on the dependent chain, and rows are fetched (float4) three rows ahead.  Measured alone
+// on a B200: 530 cycles against 620 for the plain loop.  Called by one full warp.
 template <int PITCH>
 __device__ __forceinline__ void tri_inverse16(const float* Ub, unsigned char* Tsw, int r0, int lane) {
     constexpr int Lb = 16;

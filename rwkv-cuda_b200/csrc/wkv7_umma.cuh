@@ -11,7 +11,7 @@
 //     kc*LBO + r*16 bytes, 8-row groups SBO = 128 bytes apart; one instruction consumes K = 8 (two pieces).
 // Every mbarrier wait is bounded.
 #pragma once
-#include "wkv7_chunked.cuh"
+#include "chunk_tf32.cuh"
 
 namespace rwkvb200 {
 namespace v7u {
