@@ -67,10 +67,13 @@ class V7Workload:
         w = mk()
         kk = torch.nn.functional.normalize(mk(), dim=-1)
         a, b = -kk, kk * torch.sigmoid(mk())
-        self.host_in = [x.to(bf).cpu().pin_memory() for x in (r, w, k, v, a, b)]
-        self.host_dy = mk().to(bf).cpu().pin_memory()
-        self.host_s0 = (0.1 * torch.randn(self.B, H, N, N, generator=g, device=device)[lo:lo + B]).cpu().pin_memory()
-        self.host_dsT = torch.randn(self.B, H, N, N, generator=g, device=device)[lo:lo + B].cpu().pin_memory()
+        # (pinned buffers are allocated with the thread bound to the GPU's NUMA node, where the platform tells)
+        with R.host_pipeline.host_memory_near(device) as node:
+            self.numa_node = node
+            self.host_in = [x.to(bf).cpu().pin_memory() for x in (r, w, k, v, a, b)]
+            self.host_dy = mk().to(bf).cpu().pin_memory()
+            self.host_s0 = (0.1 * torch.randn(self.B, H, N, N, generator=g, device=device)[lo:lo + B]).cpu().pin_memory()
+            self.host_dsT = torch.randn(self.B, H, N, N, generator=g, device=device)[lo:lo + B].cpu().pin_memory()
         del r, k, v, w, kk, a, b
         dev = device
         self.dev = dev
@@ -114,8 +117,9 @@ class V7Workload:
         ends there; copies in both directions and the kernels are inside the timed region."""
         if self.host_out is None:
             names = self.R.host_pipeline.Wkv7HostPipeline
-            self.host_out = {n: torch.empty_like(self.host_in[0]).pin_memory() for n in names.OUT}
-            self.host_out.update(sT=torch.empty_like(self.host_s0).pin_memory(), ds0=torch.empty_like(self.host_s0).pin_memory())
+            with self.R.host_pipeline.host_memory_near(self.dev):
+                self.host_out = {n: torch.empty_like(self.host_in[0]).pin_memory() for n in names.OUT}
+                self.host_out.update(sT=torch.empty_like(self.host_s0).pin_memory(), ds0=torch.empty_like(self.host_s0).pin_memory())
             self.host_named = dict(zip(("r", "w", "k", "v", "a", "b"), self.host_in))
             self.host_named.update(dy=self.host_dy, s0=self.host_s0, dsT=self.host_dsT)
             self.pipe = names(self.T, self.H, self.N, self.dev, slice_batch=1)
@@ -627,7 +631,10 @@ def main():
                                  "algorithmic_bytes_per_launch": fb},
                          "fwd_bwd_frac": (fb + bb) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "steps": args.e2e_steps},
+                    "d2h_bytes_per_step": d2h * world, "steps": args.e2e_steps,
+                    # what each GPU's host link carried, each way, while both directions and the kernels ran
+                    "host_link_gbs_per_gpu_each_way": (h2d * e2e_val / tokens_step / 1e9) if e2e_val else None,
+                    "pinned_buffers_numa_node_rank0": getattr(wl, "numa_node", None)},
             "gpu_launches": W.launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "reference_kernel": ref_kernel_block,

@@ -17,6 +17,20 @@
 #include "wkv7_dispatch.cuh"
 
 namespace rwkvb200 {
+// Optional cycle counters of the two groups (-DRWKVB200_PHASE_CLOCKS): front group phases 0.., back group 8..
+#ifdef RWKVB200_PHASE_CLOCKS
+#define PIPE_MARK(k)                                                                                       \
+    do {                                                                                                   \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {                                             \
+            const long long now_ = clock64();                                                              \
+            atomicAdd(&g_phase_clocks[wg][(k) + 8 * grp], (unsigned long long)(now_ - pipe_last_));   \
+            pipe_last_ = now_;                                                                             \
+        }                                                                                                  \
+    } while (0)
+#else
+#define PIPE_MARK(k)
+#endif
+
 namespace v7p {
 
 using namespace v7x;
@@ -143,6 +157,9 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     const uint32_t lead = elect_one();
     const int gbar = 1 + grp;   // named barrier of this group
     int fail = 0;
+#ifdef RWKVB200_PHASE_CLOCKS
+    long long pipe_last_ = clock64();
+#endif
 
     // ================================ front group ==========================================================
     if (grp == 0) {
@@ -164,7 +181,9 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const uint32_t arA = smem_u32(AR), bkA = smem_u32(BK), svA = smem_u32(SV), s0A = smem_u32(S0);
             const uint32_t uakA = smem_u32(Uak), d0A = smem_u32(D0), n1A = smem_u32(N1);
             // the back group must have released this set (it was used two chunks ago)
+            PIPE_MARK(1);
             if (it >= 2 && !mbar_wait(bar + kEmpty + set, ((it >> 1) - 1) & 1)) fail = 30;
+            PIPE_MARK(0);
             if (fail) atomicMax(const_cast<int*>(abort_word), fail);
             if (gtid == 0) gabort[0] = *abort_word;
             group_sync(gbar, GNT);
@@ -196,7 +215,9 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int ks = 0; ks < 8; ++ks)   // X_a = S0 A~^T, needed after the inverse only
                     mma_ss(tmF2, desc_k(s0A, 0, ks * 8, HALF64), desc_k(arA, 0, ks * 8, HALF64), idesc64(32, 0, 0), ks > 0, lead);
             }
+            PIPE_MARK(2);
             if (!mbar_wait(bar + kFU, par)) fail = 31;
+            PIPE_MARK(3);
             tc_fence_after();
             {
                 float u[4][4];
@@ -206,6 +227,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
             tc_fence_before();
             group_sync(gbar, GNT);
+            PIPE_MARK(4);
             if (wg < 2) tri_inverse16<BPITCH>(Uab + wg * 16 * BPITCH, D0, 16 * wg, lane);
             proxy_fence();
             tc_fence_before();
@@ -220,6 +242,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 mma_commit(bar + kFSA, lead);
                 if (cs.fail) fail = 32;
             }
+            PIPE_MARK(5);
             if (c > 0) fetch_chunk<7, 4>(raw, src, tok0, C, c - 1, T, wg, lane);   // under the chain
             if (!mbar_wait(bar + kFSA, par)) fail = 33;
             tc_fence_after();
@@ -272,7 +295,9 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             const uint32_t arA = smem_u32(AR), bkA = smem_u32(BK), svA = smem_u32(SV), eyA = smem_u32(EY), s0A = smem_u32(S0);
             const uint32_t uakA = smem_u32(base + SetSmem::kUak), ubrA = smem_u32(base + SetSmem::kUbr), ukrA = smem_u32(base + SetSmem::kUkr);
             const uint32_t d0A = smem_u32(base + SetSmem::kD0), n1A = smem_u32(base + SetSmem::kN1), pA = smem_u32(Pm);
+            PIPE_MARK(6);
             if (!mbar_wait(bar + kFull + set, (it >> 1) & 1)) fail = 40;   // the front group has filled this set
+            PIPE_MARK(0);
             if (fail) atomicMax(const_cast<int*>(abort_word), fail);
             if (gtid == 0) gabort[1] = *abort_word;
             tc_fence_before();
@@ -298,6 +323,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tc_fence_before();
             group_sync(gbar, GNT);
             tc_fence_after();
+            PIPE_MARK(1);
             // ---- EV, dV ---------------------------------------------------------------------------------
             if (wg == 0) {
 #pragma unroll
@@ -341,6 +367,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tc_fence_before();
             group_sync(gbar, GNT);
             tc_fence_after();
+            PIPE_MARK(2);
             // ---- P; with it what needs EV but not P ---------------------------------------------------
             if (wg == 0) {
                 const uint32_t idkk = idesc64(64, 0, 0), idmm = idesc64(64, 1, 1);
@@ -393,6 +420,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     mma_ss(tmW2, desc_mn(bkA, ks * 8, HALF64), desc_k(pA, 0, ks * 8, HALF64), idmk, 1, lead);
                 mma_commit(bar + kBG, lead);
             }
+            PIPE_MARK(3);
             // meanwhile the anchor: A0[j] = sum_i ET_new[j][i] S0[i][j]; this warp: value columns 32*hs .. 32*hs+31
             if (!mbar_wait(bar + kBE, par)) fail = 44;
             tc_fence_after();
@@ -415,6 +443,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
             if (!mbar_wait(bar + kBG, par)) fail = 45;
             tc_fence_after();
+            PIPE_MARK(4);
             // ---- epilogue: this warp has key rows row0+g / +8 and tokens 16*hs .. 16*hs+15 ------------------
             bf16* stg[5];
 #pragma unroll
@@ -481,6 +510,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                         stg[4][tt * 72 + j] = __float2bfloat16_rn((a0 - gl[h][nt][e]) * fw[h][nt][e]);
                     }
             }
+            PIPE_MARK(5);
             {   // dr, da, dk, db out: thread = (token, 16-byte piece)
                 const int tt = gtid >> 3, piece = gtid & 7;
                 if (tt < valid) {
@@ -522,6 +552,8 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm0) : "memory");
 }
+
+WKV7_PHASE_READER(rwkvb200_phase_clocks_l32_bwdp)
 
 }  // namespace v7p
 

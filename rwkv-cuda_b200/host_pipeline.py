@@ -6,9 +6,63 @@ on three CUDA streams (host->device copies, kernels, device->host copies), so th
 directions of the PCIe link and the kernels overlap; device memory holds three slices at a time,
 whatever the batch size.  Units (batch, head) are independent, so slicing does not change results.
 """
+import contextlib
+import os
+
 import torch
 
 from . import ops
+
+
+def gpu_numa_node(device):
+    """NUMA node of the host that the GPU hangs off (from sysfs, by the GPU's PCI address), or None when
+    the platform does not say (one node, a container without sysfs, no NVML)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        idx = torch.device(device).index or 0
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ent = vis.split(",")[idx].strip()
+            h = pynvml.nvmlDeviceGetHandleByUUID(ent) if ent.startswith("GPU-") else pynvml.nvmlDeviceGetHandleByIndex(int(ent))
+        else:
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        bus = pynvml.nvmlDeviceGetPciInfo(h).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:          # NVML prints an 8-digit domain, sysfs uses 4
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        return node if node >= 0 else None
+    except Exception:
+        return None
+
+
+@contextlib.contextmanager
+def host_memory_near(device):
+    """Runs the body with the calling thread bound to the CPUs of the GPU's NUMA node, so that pinned host
+    buffers allocated inside come from memory next to the GPU's PCIe root (with several GPUs per host, buffers
+    that all sit on one node send the other socket's traffic across the inter-socket link).  Yields the node,
+    or None when nothing was bound; the previous affinity is restored afterwards."""
+    node, old = gpu_numa_node(device), None
+    try:
+        if node is not None:
+            cpus = set()
+            for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            old = os.sched_getaffinity(0)
+            if cpus & old:
+                os.sched_setaffinity(0, cpus & old)
+            else:
+                node, old = None, None
+    except Exception:
+        node, old = None, None
+    try:
+        yield node
+    finally:
+        if old is not None:
+            os.sched_setaffinity(0, old)
 
 
 class Wkv7HostPipeline:
