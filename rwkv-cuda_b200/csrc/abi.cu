@@ -144,9 +144,11 @@ extern "C" int rwkvb200_wkv7_forward(int dtype, int B, int T, int H, int N, int 
         RWKV_REQUIRE(aligned16({s0, r, w, k, v, a, b, y, sT, s, sa}), RWKVB200_EALIGN,
                      "wkv7_forward: the bf16 N=64 path needs 16-byte aligned tensors");
         const int form = g_wkv7_bwd_form.load(), expire = g_wkv7_test_expire.exchange(0);
-        // at most one unit per SM: the two-stage form (see the backward) shortens the chain of chunks
-        if (!expire && (form == 2 || (form == 0 && (long long)B * H <= sm_count())))
-            return wkv7_l32_forward_pipelined(B, T, H, s0, r, w, k, v, a, b, y, sT, s, as_stream(stream));
+        // the staged form (three warp groups on consecutive chunks, inputs by TMA) is the faster one at every size
+        if (!expire && form != 1) {
+            const int rc = wkv7_l32_forward_pipelined(B, T, H, s0, r, w, k, v, a, b, y, sT, s, as_stream(stream));
+            if (rc != 1) return rc;   // 1: no tensor maps on this driver, use the one-group kernel
+        }
         return wkv7_l32_forward(B, T, H, s0, r, w, k, v, a, b, y, sT, s, expire, as_stream(stream));
     }
     return wkv7_generic_forward(dtype, B, T, H, N, chunk_len, s0, r, w, k, v, a, b, y, sT, s, sa, as_stream(stream));

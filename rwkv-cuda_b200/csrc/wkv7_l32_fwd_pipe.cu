@@ -1,60 +1,97 @@
-// RWKV-7 forward, head size 64, bf16 activations, 32-token chunks on tcgen05: the two-stage form.
+// RWKV-7 forward, head size 64, bf16 activations, 32-token chunks on tcgen05: the staged form.
 //
-// Same algorithm and the same products as wkv7_l32_fwd.cu, split over two groups of 4 warps that work on
+// Same algorithm and the same products as wkv7_l32_fwd.cu, split over three groups of 4 warps that work on
 // consecutive chunks at the same time:
-//   front group, chunk c+1: operand preparation, U, the masked matrices and the block inverses
-//                           (nothing of it needs the carried state);
-//   back group, chunk c:    the dependent chain X, Z, SA, Y and the state update, y out, decay scaling.
-// Two sets of operand arrays are handed over through mbarriers (full / empty); inside a group the warps
-// synchronise on a named barrier.  One thread block per SM (133 KB of shared memory, 256 columns of
-// tensor memory); chosen for launches with at most one (batch, head) unit per SM, where the time is one
-// unit's chain of chunks.
+//   loader group, chunk c+2:  the raw rows of the six input tensors arrive as tiled bulk copies (TMA, one
+//                             [32 tokens][64 channels] tile per tensor and chunk, two chunks ahead); operand
+//                             preparation ([A~;R~], [B~;K~], V, chunk decay);
+//   matrix group, chunk c+1:  U on the tensor core, the masked matrices and the block inverses
+//                             (nothing of either group needs the carried state);
+//   chain group, chunk c:     the dependent chain X, Z, SA, Y and the state update, y out, decay scaling.
+// Three sets of operand arrays and two sets of token x token matrices are handed on through mbarriers
+// (full / empty; an operand set is released by the matrix group and by the chain group); inside a group the
+// warps synchronise on a named barrier.  One thread block per SM (220 KB of shared memory, 256 columns of
+// tensor memory).  Measured per chunk: loader 3.7 k cycles, matrix group 3.1 k, chain group 3.4 k, against
+// 7.2 k for one thread block of wkv7_l32_fwd.cu alone and 11 k with three on an SM (3.7 k per chunk and SM):
+// B = 16, T = 4096 1.78 ms against 1.94 ms, B = 2 0.27 ms against 0.48 ms.  What did not help: the 192 rows of
+// a chunk as untiled bulk copies of 128 bytes (the copy engine takes about 60 cycles per copy: 13 k cycles per
+// chunk), the chunk after next requested with plain loads into a second register set (the 48 loads take
+// 1.7 k cycles to issue), eight loader warps (preparation 3.9 k instead of 3.3 k), the six tiles issued by
+// six lanes instead of one.
+#include <cuda.h>
+
 #include "wkv7_l32.cuh"
 #include "wkv7_dispatch.cuh"
 
 namespace rwkvb200 {
+// Optional cycle counters of the groups (-DRWKVB200_PHASE_CLOCKS): group g uses phases 5g .. 5g+4
+#ifdef RWKVB200_PHASE_CLOCKS
+#define PIPE_MARK(k)                                                                                       \
+    do {                                                                                                   \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {                                             \
+            const long long now_ = clock64();                                                              \
+            atomicAdd(&g_phase_clocks[wg][(k) + 5 * grp], (unsigned long long)(now_ - pipe_last_));        \
+            pipe_last_ = now_;                                                                             \
+        }                                                                                                  \
+    } while (0)
+#else
+#define PIPE_MARK(k)
+#endif
+
 namespace v7q {
 
 using namespace v7x;
 
 constexpr int GNT = 128;          // threads per group
-constexpr int PNT = 2 * GNT;
+constexpr int PNT = 3 * GNT;
+constexpr int NA = 3;             // operand sets in flight
+constexpr int NU = 2;             // matrix sets in flight
+constexpr int NS = 2;             // chunks of raw input rows in flight (bulk copies)
 
-struct SetSmem {
-    static constexpr int kAR = 0;
-    static constexpr int kBK = kAR + ARR64;
-    static constexpr int kV = kBK + ARR64;
-    static constexpr int kUak = kV + ARR32;
-    static constexpr int kUbr = kUak + HALF32;
-    static constexpr int kUkr = kUbr + HALF32;
-    static constexpr int kD0 = kUkr + HALF32;
-    static constexpr int kN1 = kD0 + HALF32;
-    static constexpr int kUab = kN1 + HALF32;           // plain [32][UPITCH] (front group only)
-    static constexpr int kWe = kUab + 32 * UPITCH * 4;
-    static constexpr int kHs = kWe + 256;               // [4][64] (front group only)
-    static constexpr int kBytes = (kHs + 1024 + 1023) / 1024 * 1024;
-};
 struct PipeSmem {
-    static constexpr int kSet1 = SetSmem::kBytes;
-    static constexpr int kY = 2 * SetSmem::kBytes;      // bf16 [32][72]
-    static constexpr int kBar = kY + 32 * 72 * 2;       // 10 mbarriers, tmem slot, abort words
-    static constexpr int kBytes = kBar + 128 + 1024;
+    static constexpr int kASet = 2 * ARR64 + ARR32;     // [A~;R~], [B~;K~], V
+    static constexpr int kUSet = 5 * HALF32;            // U_ak, U_br, U_kr, D0, N1
+    static constexpr int kU = NA * kASet;
+    static constexpr int kWe = kU + NU * kUSet;         // chunk decay, one row of 64 floats per operand set
+    static constexpr int kHs = kWe + NA * 256;          // [4][64] scratch of the loader group
+    static constexpr int kUab = kHs + 1024;             // plain [32][UPITCH], scratch of the matrix group
+    static constexpr int kY = kUab + 32 * UPITCH * 4;   // bf16 [32][72]
+    static constexpr int kRaw = (kY + 32 * 72 * 2 + 127) / 128 * 128;   // raw input rows: [NS][6 tensors][32 tokens][64 bf16]
+    static constexpr int kBar = kRaw + NS * 6 * 32 * 128;         // mbarriers, tmem slot, abort words
+    static constexpr int kBytes = kBar + 256 + 1024;
 };
-static_assert(PipeSmem::kBar % 8 == 0 && PipeSmem::kBytes <= 232448, "layout");
+static_assert(PipeSmem::kASet % 1024 == 0 && PipeSmem::kUSet % 1024 == 0 && PipeSmem::kBytes <= 232448, "layout");
 
 __device__ int g_l32_fwdp_error = 0;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One [32 tokens][64 channels] bf16 tile of a (B*T, C) tensor -> shared memory (plain rows of 128 bytes) by the
+// copy engine; x = first channel (a multiple of 8), y = first row; completion is counted in bytes on the mbarrier.
+__device__ __forceinline__ void tma_tile(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+struct InputMaps {
+    CUtensorMap m[6];   // r, w, k, v, a, b as (B*T, C) bf16, box 64 x 32
+};
+__device__ __forceinline__ void mbar_init_count(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
 
-// mbarriers: 0-1 full[set], 2-3 empty[set]; front: 4 U; back: 5 Y, 6 S, 7 its chain
-enum { kFull = 0, kEmpty = 2, kFU = 4, kBY = 5, kBS = 6, kBChain = 7, kNBar = 8 };
+// mbarriers: operand set full (loader -> matrix group) / empty (two arrivals: matrix and chain group);
+// matrix set full (matrix -> chain group; it implies the operand set) / empty; U done; Y, S done; the chain's own
+enum { kFullA = 0, kEmptyA = kFullA + NA, kFullU = kEmptyA + NA, kEmptyU = kFullU + NU, kFU = kEmptyU + NU, kBY, kBS, kBChain,
+       kRawFull, kNBar = kRawFull + NS };
 
 __global__ void __launch_bounds__(PNT, 1)
-wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __restrict__ r_,
-                     const bf16* __restrict__ w_, const bf16* __restrict__ k_, const bf16* __restrict__ v_,
-                     const bf16* __restrict__ a_, const bf16* __restrict__ b_, bf16* __restrict__ y_,
+wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_constant__ InputMaps maps, bf16* __restrict__ y_,
                      float* __restrict__ sT_, float* __restrict__ ck_) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -62,7 +99,7 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + PipeSmem::kBar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + kNBar);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* gabort = abort_word + 1;
+    volatile int* gabort = abort_word + 1;   // one copy per group, so that a group takes its decision on one value
 
     const int hh = blockIdx.x, bb = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -74,21 +111,20 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     const i64 sbase = (i64)(bb * H + hh) * 64 * 64;
     const int nchunks = (T + LC - 1) / LC;
     float* ck = ck_ ? ck_ + (i64)(bb * H + hh) * (T / 16) * 64 * 64 : nullptr;
-    const bf16* src[6] = {r_, w_, k_, v_, a_, b_};
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < kNBar; ++i) mbar_init(bar + i);
-        *abort_word = 0; gabort[0] = 0; gabort[1] = 0;
+        for (int i = 0; i < kNBar; ++i) mbar_init_count(bar + i, (i >= kEmptyA && i < kEmptyA + NA) ? 2 : 1);
+        *abort_word = 0; gabort[0] = 0; gabort[1] = 0; gabort[2] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(smem_u32(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = tid; i < 2 * HALF32 / 4; i += PNT) {   // D0 and N1 of both sets: the blocks never written stay zero
-        reinterpret_cast<float*>(smem + SetSmem::kD0)[i] = 0.f;
-        reinterpret_cast<float*>(smem + PipeSmem::kSet1 + SetSmem::kD0)[i] = 0.f;
+    for (int i = tid; i < NU * 2 * HALF32 / 4; i += PNT) {   // D0 and N1 of every matrix set: the blocks never written stay zero
+        const int u = i / (2 * HALF32 / 4), j = i % (2 * HALF32 / 4);
+        reinterpret_cast<float*>(smem + PipeSmem::kU + u * PipeSmem::kUSet + 3 * HALF32)[j] = 0.f;
     }
     tc_fence_before();
     __syncthreads();
@@ -99,38 +135,97 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     const uint32_t lead = elect_one();
     const int gbar = 1 + grp;
     int fail = 0;
+#ifdef RWKVB200_PHASE_CLOCKS
+    long long pipe_last_ = clock64();
+#endif
 
     if (grp == 0) {
-        // ================================ front group ======================================================
-        RawChunk<6, 8> raw;
-        fetch_chunk<6, 8>(raw, src, tok0, C, 0, T, wg, lane);
-        uint32_t par = 0;
-        for (int c = 0; c < nchunks; ++c, par ^= 1) {
-            const int set = c & 1, valid = min(LC, T - c * LC);
-            unsigned char* base = smem + set * PipeSmem::kSet1;
-            unsigned char *AR = base + SetSmem::kAR, *BK = base + SetSmem::kBK, *Vs = base + SetSmem::kV;
-            unsigned char *Uak = base + SetSmem::kUak, *Ubr = base + SetSmem::kUbr, *Ukr = base + SetSmem::kUkr;
-            unsigned char *D0 = base + SetSmem::kD0, *N1 = base + SetSmem::kN1;
-            float* Uab = reinterpret_cast<float*>(base + SetSmem::kUab);
-            float* We = reinterpret_cast<float*>(base + SetSmem::kWe);
-            float* Hs = reinterpret_cast<float*>(base + SetSmem::kHs);
-            if (c >= 2 && !mbar_wait(bar + kEmpty + set, ((c >> 1) - 1) & 1)) fail = 30;   // the back group released this set
+        // ================================ loader group =====================================================
+        float* Hs = reinterpret_cast<float*>(smem + PipeSmem::kHs);
+        // The raw rows of a chunk (6 tensors x 32 tokens x 128 bytes) come in as six tiled bulk copies (TMA), issued
+        // by one thread two chunks ahead and counted on an mbarrier; every thread then takes its part (a channel
+        // pair of 8 tokens per tensor) into registers.  Rows beyond the sequence belong to the next batch row or
+        // lie outside the tensor (read as zeros); they are masked when the registers are filled.
+        unsigned char* stg = smem + PipeSmem::kRaw;
+        int issued = 0;
+        auto issue_raw = [&](int c) {
+            const int st = c & 1;
+            uint64_t* fb = bar + kRawFull + st;
+            if (lane == 0) {
+                mbar_expect_tx(fb, 6 * 32 * 128);
+#pragma unroll
+                for (int x = 0; x < 6; ++x) tma_tile(stg + (st * 6 + x) * 32 * 128, &maps.m[x], hh * 64, bb * T + c * LC, fb);
+            }
+            issued = c + 1;
+        };
+        if (wg == 0) {
+            issue_raw(0);
+            if (nchunks > 1) issue_raw(1);
+        }
+        int sa = 0, ua = 0;   // operand set of this chunk, how often it has been used before
+        int c = 0;
+        for (; c < nchunks; ++c) {
+            const int valid = min(LC, T - c * LC), st = c & 1;
+            unsigned char* A = smem + sa * PipeSmem::kASet;
+            float* We = reinterpret_cast<float*>(smem + PipeSmem::kWe + sa * 256);
+            PIPE_MARK(2);
+            if (!mbar_wait(bar + kRawFull + st, (c >> 1) & 1)) fail = 31;                 // the rows have arrived
+            if (ua >= 1 && !mbar_wait(bar + kEmptyA + sa, (ua - 1) & 1)) fail = 30;       // both consumers released this set
+            PIPE_MARK(0);
+            RawChunk<6, 8> raw;
+#pragma unroll
+            for (int x = 0; x < 6; ++x)
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int tt = 8 * wg + q;
+                    raw.x[x][q] = tt < valid ? *reinterpret_cast<const uint32_t*>(stg + ((st * 6 + x) * 32 + tt) * 128 + 4 * lane) : 0u;
+                }
+            PIPE_MARK(3);
             if (fail) atomicMax(const_cast<int*>(abort_word), fail);
             if (gtid == 0) gabort[0] = *abort_word;
-            group_sync(gbar, GNT);
+            group_sync(gbar, GNT);   // (every thread has taken its part of the rows: the stage may be refilled)
             if (gabort[0]) break;
-            prepare_operands<6, 8, 4>(raw, valid, AR, BK, Vs, HALF32, nullptr, 0, We, Hs, nullptr, wg, lane, gbar);
+            if (wg == 0 && c + NS < nchunks) issue_raw(c + NS);
+            PIPE_MARK(4);
+            prepare_operands<6, 8, 4>(raw, valid, A, A + ARR64, A + 2 * ARR64, HALF32, nullptr, 0, We, Hs, nullptr, wg, lane, gbar);
             proxy_fence();
+            group_sync(gbar, GNT);
+            if (gtid == 0) mbar_arrive(bar + kFullA + sa);
+            PIPE_MARK(1);
+            if (++sa == NA) { sa = 0; ++ua; }
+        }
+        if (fail) atomicMax(const_cast<int*>(abort_word), fail);
+        // leaving early: the copies that are still in flight must have landed before the block may end
+        if (wg == 0)
+            for (int cc = c; cc < issued; ++cc) mbar_wait(bar + kRawFull + (cc & 1), (cc >> 1) & 1);
+    } else if (grp == 1) {
+        // ================================ matrix group =====================================================
+        float* Uab = reinterpret_cast<float*>(smem + PipeSmem::kUab);
+        int sa = 0, ua = 0;
+        uint32_t par = 0;
+        for (int c = 0; c < nchunks; ++c, par ^= 1) {
+            const int su = c & 1;
+            unsigned char* A = smem + sa * PipeSmem::kASet;
+            unsigned char* U = smem + PipeSmem::kU + su * PipeSmem::kUSet;
+            unsigned char *Uak = U, *Ubr = U + HALF32, *Ukr = U + 2 * HALF32, *D0 = U + 3 * HALF32, *N1 = U + 4 * HALF32;
+            PIPE_MARK(4);
+            if (!mbar_wait(bar + kFullA + sa, ua & 1)) fail = 35;                              // operands of this chunk
+            if (c >= NU && !mbar_wait(bar + kEmptyU + su, ((c >> 1) - 1) & 1)) fail = 36;      // the chain group released this matrix set
+            PIPE_MARK(0);
+            if (fail) atomicMax(const_cast<int*>(abort_word), fail);
+            if (gtid == 0) gabort[1] = *abort_word;
             tc_fence_before();
             group_sync(gbar, GNT);
             tc_fence_after();
+            if (gabort[1]) break;
             if (wg == 0) {
-                issue_u(tmU, smem_u32(AR), smem_u32(BK), lead);
+                issue_u(tmU, smem_u32(A), smem_u32(A + ARR64), lead);
                 mma_commit(bar + kFU, lead);
             }
-            if (c + 1 < nchunks) fetch_chunk<6, 8>(raw, src, tok0, C, c + 1, T, wg, lane);   // under U
-            if (!mbar_wait(bar + kFU, par)) fail = 31;
+            if (!mbar_wait(bar + kFU, par)) fail = 37;
             tc_fence_after();
+            if (gtid == 0) mbar_arrive(bar + kEmptyA + sa);   // this group is done with the operand set
+            PIPE_MARK(1);
             {
                 float u[8][4];
                 tmem_ld_tiles<8>(u, tmU + lane_off);
@@ -139,14 +234,17 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             }
             tc_fence_before();
             group_sync(gbar, GNT);
+            PIPE_MARK(2);
             if (wg < 2) tri_inverse16<UPITCH>(Uab + 16 * wg * (UPITCH + 1), D0, 16 * wg, lane);
             proxy_fence();
             group_sync(gbar, GNT);
-            if (gtid == 0) mbar_arrive(bar + kFull + set);   // the set is complete
+            if (gtid == 0) mbar_arrive(bar + kFullU + su);   // the matrix set is complete
+            PIPE_MARK(3);
+            if (++sa == NA) { sa = 0; ++ua; }
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
     } else {
-        // ================================ back group =======================================================
+        // ================================ chain group ======================================================
         {   // initial state -> tensor memory (and saved as the start state of chunk 0)
             float Sd[8][4];
 #pragma unroll
@@ -166,21 +264,25 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             tmem_wait_st();
         }
         ChainSync cs{bar + kBChain, 0, 0};
+        int sa = 0;
         uint32_t par = 0;
         for (int c = 0; c < nchunks; ++c, par ^= 1) {
-            const int set = c & 1, valid = min(LC, T - c * LC);
-            unsigned char* base = smem + set * PipeSmem::kSet1;
-            const float* We = reinterpret_cast<const float*>(base + SetSmem::kWe);
-            const uint32_t arA = smem_u32(base + SetSmem::kAR), bkA = smem_u32(base + SetSmem::kBK), vA = smem_u32(base + SetSmem::kV);
-            const uint32_t uakA = smem_u32(base + SetSmem::kUak), ubrA = smem_u32(base + SetSmem::kUbr), ukrA = smem_u32(base + SetSmem::kUkr);
-            const uint32_t d0A = smem_u32(base + SetSmem::kD0), n1A = smem_u32(base + SetSmem::kN1);
-            if (!mbar_wait(bar + kFull + set, (c >> 1) & 1)) fail = 40;   // the front group has filled this set
+            const int su = c & 1, valid = min(LC, T - c * LC);
+            unsigned char* A = smem + sa * PipeSmem::kASet;
+            unsigned char* U = smem + PipeSmem::kU + su * PipeSmem::kUSet;
+            const float* We = reinterpret_cast<const float*>(smem + PipeSmem::kWe + sa * 256);
+            const uint32_t arA = smem_u32(A), bkA = smem_u32(A + ARR64), vA = smem_u32(A + 2 * ARR64);
+            const uint32_t uakA = smem_u32(U), ubrA = smem_u32(U + HALF32), ukrA = smem_u32(U + 2 * HALF32);
+            const uint32_t d0A = smem_u32(U + 3 * HALF32), n1A = smem_u32(U + 4 * HALF32);
+            PIPE_MARK(4);
+            if (!mbar_wait(bar + kFullU + su, (c >> 1) & 1)) fail = 40;   // matrices (and with them the operands) of this chunk
+            PIPE_MARK(0);
             if (fail) atomicMax(const_cast<int*>(abort_word), fail);
-            if (gtid == 0) gabort[1] = *abort_word;
+            if (gtid == 0) gabort[2] = *abort_word;
             tc_fence_before();
             group_sync(gbar, GNT);
             tc_fence_after();
-            if (gabort[1]) break;
+            if (gabort[2]) break;
             if (wg == 0) {
                 const uint32_t id64 = idesc64(64, 0, 0);
 #pragma unroll
@@ -210,6 +312,7 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             }
             if (!mbar_wait(bar + kBY, par)) fail = 42;
             tc_fence_after();
+            PIPE_MARK(1);
             {
                 float Y[4][4];
                 tmem_ld_tiles<4>(Y, tmX + 32 + lane_off);
@@ -234,6 +337,7 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             }
             if (!mbar_wait(bar + kBS, par)) fail = 43;
             tc_fence_after();
+            PIPE_MARK(2);
             {
                 float* dst = (c + 1 < nchunks) ? (ck ? ck + (i64)(c + 1) * 64 * 64 : nullptr) : (sT_ ? sT_ + sbase : nullptr);
                 float Sd[8][4];
@@ -253,7 +357,12 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
             }
             tc_fence_before();
             group_sync(gbar, GNT);
-            if (gtid == 0) mbar_arrive(bar + kEmpty + set);   // the front group may refill this set
+            if (gtid == 0) {   // the other groups may refill the sets
+                mbar_arrive(bar + kEmptyA + sa);
+                mbar_arrive(bar + kEmptyU + su);
+            }
+            PIPE_MARK(3);
+            if (++sa == NA) sa = 0;
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
     }
@@ -265,17 +374,51 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tm0) : "memory");
 }
 
+WKV7_PHASE_READER(rwkvb200_phase_clocks_l32_fwdp)
+
 }  // namespace v7q
 
+namespace {
+// cuTensorMapEncodeTiled through the runtime's driver entry point query (the library links the runtime only)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, 32};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+// Returns RWKVB200_OK, an error code, or 1 when tensor maps cannot be made here (no entry point in the driver, or a
+// shape it refuses): the caller then uses the one-group kernel.
 int wkv7_l32_forward_pipelined(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k, const void* v,
                                const void* a, const void* b, void* y, float* sT, float* s, cudaStream_t st) {
     using namespace v7q;
+    if (encode_tiled() == nullptr) return 1;
+    InputMaps maps;
+    const void* in[6] = {r, w, k, v, a, b};
+    for (int x = 0; x < 6; ++x)
+        if (!make_map(&maps.m[x], in[x], (uint64_t)B * T, (uint64_t)H * 64)) return 1;
     cudaError_t e = cudaFuncSetAttribute(wkv7q_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PipeSmem::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv7_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     dim3 grid(H, B);
-    wkv7q_forward_kernel<<<grid, PNT, PipeSmem::kBytes, st>>>(T, H, s0, (const bf16*)r, (const bf16*)w, (const bf16*)k,
-                                                             (const bf16*)v, (const bf16*)a, (const bf16*)b, (bf16*)y, sT, s);
-    return check_launch("wkv7_forward(tcgen05, 32-token chunks, two stages)");
+    wkv7q_forward_kernel<<<grid, PNT, PipeSmem::kBytes, st>>>(T, H, s0, maps, (bf16*)y, sT, s);
+    return check_launch("wkv7_forward(tcgen05, 32-token chunks, three stages)");
 }
 
 int wkv7_l32_fwdp_error(int clear) {
