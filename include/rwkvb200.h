@@ -228,14 +228,16 @@ int rwkvb200_wkv7_state_update(int dtype, int B, int T, int H, int N, float* sta
  * kernels: transposed state at the end of every chunk_len tokens, and sa).  No counterpart in the
  * reference. */
 int rwkvb200_wkv7_select_path(int path);
-/* Form of the tensor-core RWKV-7 kernels: 0 = automatic (two-stage kernels for launches with at most one
- * (batch, head) unit per SM, one-group kernels otherwise), 1 = one-group kernels, 2 = two-stage kernels.
- * Both run the same products; results agree to the last bf16 digit (a few dw elements differ by one ulp).
+/* Form of the tensor-core RWKV-7 kernels: 0 = automatic (forward: the staged kernel, three warp groups on
+ * consecutive chunks with inputs by TMA; backward: the two-stage kernel for launches with at most one
+ * (batch, head) unit per SM, the one-group kernel otherwise), 1 = one-group kernels, 2 = staged / two-stage
+ * kernels.  All run the same products; results agree to the last bf16 digit (a few dw elements differ by one ulp).
  * Process-wide; no counterpart in the reference. */
 int rwkvb200_wkv7_select_form(int form);
 /* Synchronous read of the current device's sticky status word: 0, or 10 + n / 20 + n when the n-th
  * bounded wait of the tensor-core forward / backward ran out in some thread block (30.. / 40..: the
- * front / back warp group of the two-stage backward, 50.. / 60.. of the two-stage forward) (the outputs of
+ * front / back warp group of the two-stage backward, 50.. / 55.. / 60..: loader / matrix / chain group of the
+ * staged forward) (the outputs of
  * that call are then invalid); negative on a CUDA error.  Per device; stays set until cleared. */
 int rwkvb200_device_status(void);
 /* Resets the current device's status word.  No counterpart in the reference. */

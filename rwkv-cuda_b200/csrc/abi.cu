@@ -50,7 +50,7 @@ extern "C" int rwkvb200_built_for_sm(void) { return 100; }
 // must see the same value (the saved buffers differ between the two kernel families).
 static std::atomic<int> g_wkv7_path{0};
 static std::atomic<int> g_wkv7_test_expire{0};
-static std::atomic<int> g_wkv7_bwd_form{0};   // 0 automatic, 1 one-group kernels, 2 two-stage kernels
+static std::atomic<int> g_wkv7_bwd_form{0};   // 0 automatic, 1 one-group kernels, 2 staged forward / two-stage backward
 
 static int sm_count() {
     constexpr int kMaxDevices = 64;
@@ -191,6 +191,12 @@ extern "C" int rwkvb200_wkv7_state_update(int dtype, int B, int T, int H, int N,
     // (decoding steps, odd lengths, other head sizes, fp32) the general-shape kernel
     const bool tensor = g_wkv7_path.load() != 1 && dtype == RWKVB200_BF16 && N == 64 && T % 16 == 0 && T >= 64 &&
                         aligned16({state, r, w, k, v, a, b, y});
-    if (tensor) return wkv7_l32_forward(B, T, H, state, r, w, k, v, a, b, y, state, nullptr, 0, as_stream(stream));
+    if (tensor) {
+        if (g_wkv7_bwd_form.load() != 1) {
+            const int rc = wkv7_l32_forward_pipelined(B, T, H, state, r, w, k, v, a, b, y, state, nullptr, as_stream(stream));
+            if (rc != 1) return rc;   // 1: no tensor maps on this driver, use the one-group kernel
+        }
+        return wkv7_l32_forward(B, T, H, state, r, w, k, v, a, b, y, state, nullptr, 0, as_stream(stream));
+    }
     return wkv7_generic_forward(dtype, B, T, H, N, T, state, r, w, k, v, a, b, y, state, nullptr, nullptr, as_stream(stream));
 }
