@@ -166,6 +166,21 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         RawChunk<7, 4> raw;
         fetch_chunk<7, 4>(raw, src, tok0, C, nchunks - 1, T, wg, lane);
         ChainSync cs{bar + kFChain, 0, 0};   // used by the group's warp 0 only
+        // dr, da, dk, db, dw of chunk cp, staged as bf16 rows by the back group in dead arrays of the set at
+        // `sbase_`, go to global memory from this group (thread = token, 16-byte piece), which has the time.
+        auto flush_outputs = [&](unsigned char* sbase_, int cp) {
+            const int tt = gtid >> 3, piece = gtid & 7;
+            if (tt < min(LC, T - cp * LC)) {
+                const bf16* st0 = reinterpret_cast<const bf16*>(sbase_ + SetSmem::kSV) + tt * 72 + piece * 8;
+                const bf16* st3 = reinterpret_cast<const bf16*>(sbase_ + SetSmem::kP) + tt * 72 + piece * 8;
+                const i64 o = tok0 + (i64)(cp * LC + tt) * C + piece * 8;
+                *reinterpret_cast<uint4*>(dr_ + o) = *reinterpret_cast<const uint4*>(st0);
+                *reinterpret_cast<uint4*>(da_ + o) = *reinterpret_cast<const uint4*>(st0 + 32 * 72);
+                *reinterpret_cast<uint4*>(dk_ + o) = *reinterpret_cast<const uint4*>(st0 + 2 * 32 * 72);
+                *reinterpret_cast<uint4*>(db_ + o) = *reinterpret_cast<const uint4*>(st3);
+                *reinterpret_cast<uint4*>(dw_ + o) = *reinterpret_cast<const uint4*>(st3 + 32 * 72);
+            }
+        };
         uint32_t par = 0;
         int it = 0;
         for (int c = nchunks - 1; c >= 0; --c, ++it, par ^= 1) {
@@ -188,6 +203,10 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             if (gtid == 0) gabort[0] = *abort_word;
             group_sync(gbar, GNT);
             if (gabort[0]) break;
+            if (it >= 2) {   // the set holds the staged outputs of the chunk that used it last: they leave from here
+                flush_outputs(base, c + 2);
+                group_sync(gbar, GNT);
+            }
             {   // chunk-start state -> S0 (swizzled), 16-byte pieces
                 const float* s0g = ck + (i64)c * 64 * 64;
 #pragma unroll
@@ -264,6 +283,15 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             if (gtid == 0) mbar_arrive(bar + kFull + set);   // the set is complete
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
+        // the outputs of the last two chunks (iterations nchunks-2 and nchunks-1 of the back group)
+        for (int j = max(0, nchunks - 2); j < nchunks && !fail; ++j) {
+            if (!mbar_wait(bar + kEmpty + (j & 1), (j >> 1) & 1)) { fail = 34; atomicMax(const_cast<int*>(abort_word), fail); }
+            if (gtid == 0) gabort[0] = *abort_word;
+            group_sync(gbar, GNT);
+            if (gabort[0]) break;
+            flush_outputs(smem + (j & 1) * PipeSmem::kSet1, nchunks - 1 - j);
+            group_sync(gbar, GNT);
+        }
     }
 
     // ================================ back group ===========================================================
@@ -511,23 +539,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     }
             }
             PIPE_MARK(5);
-            {   // dr, da, dk, db out: thread = (token, 16-byte piece)
-                const int tt = gtid >> 3, piece = gtid & 7;
-                if (tt < valid) {
-                    const i64 o = tok0 + (i64)(c * LC + tt) * C + piece * 8;
-                    *reinterpret_cast<uint4*>(dr_ + o) = *reinterpret_cast<const uint4*>(stg[0] + tt * 72 + piece * 8);
-                    *reinterpret_cast<uint4*>(da_ + o) = *reinterpret_cast<const uint4*>(stg[1] + tt * 72 + piece * 8);
-                    *reinterpret_cast<uint4*>(dk_ + o) = *reinterpret_cast<const uint4*>(stg[2] + tt * 72 + piece * 8);
-                    *reinterpret_cast<uint4*>(db_ + o) = *reinterpret_cast<const uint4*>(stg[3] + tt * 72 + piece * 8);
-                }
-            }
-            group_sync(gbar, GNT);
-            {
-                const int tt = gtid >> 3, piece = gtid & 7;
-                if (tt < valid)
-                    *reinterpret_cast<uint4*>(dw_ + tok0 + (i64)(c * LC + tt) * C + piece * 8) = *reinterpret_cast<const uint4*>(stg[4] + tt * 72 + piece * 8);
-            }
-            group_sync(gbar, GNT);
+            group_sync(gbar, GNT);   // all five staged tensors are complete: the front group stores them and refills the set
             if (gtid == 0) mbar_arrive(bar + kEmpty + set);   // the front group may refill this set
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
