@@ -17,7 +17,8 @@
 // a chunk as untiled bulk copies of 128 bytes (the copy engine takes about 60 cycles per copy: 13 k cycles per
 // chunk), the chunk after next requested with plain loads into a second register set (the 48 loads take
 // 1.7 k cycles to issue), eight loader warps (preparation 3.9 k instead of 3.3 k), the six tiles issued by
-// six lanes instead of one.
+// six lanes instead of one, two loader groups on alternate chunks (16 warps: every group then waits on another,
+// 4.0 k cycles per chunk; a third set of matrices to decouple them does not fit the shared memory).
 #include <cuda.h>
 
 #include "wkv7_l32.cuh"
