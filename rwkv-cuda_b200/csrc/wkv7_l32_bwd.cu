@@ -480,7 +480,10 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         WKV7_PHASE(14);  // dw out
     }
 
-    if (fail && tid == 0) atomicMax(&g_l32_bwd_error, fail);
+    if (fail && tid == 0) {   // a wait ran out: record it and poison this unit's outputs so that they cannot pass as results
+        atomicMax(&g_l32_bwd_error, fail);
+        dr_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

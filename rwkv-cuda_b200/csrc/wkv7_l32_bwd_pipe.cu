@@ -549,7 +549,10 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     __syncthreads();
     tc_fence_after();
     const int ab = *abort_word;
-    if (ab && tid == 0) atomicMax(&g_l32_bwdp_error, ab);
+    if (ab && tid == 0) {   // a wait ran out: record it and poison this unit's outputs so that they cannot pass as results
+        atomicMax(&g_l32_bwdp_error, ab);
+        dr_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
+    }
     if (!ab && grp == 1 && ds0_ != nullptr) {
         float Ed[4][4];
         tmem_ld_tiles<4>(Ed, tmE + 32 * hs + lane_off);

@@ -243,7 +243,11 @@ wkv7x_forward_kernel(int T, int H, const float* __restrict__ s0_, const bf16* __
         WKV7_PHASE(10);  // decay scaling, saved state
     }
 
-    if (fail && tid == 0) atomicMax(&g_l32_fwd_error, fail);
+    if (fail && tid == 0) {   // a wait ran out: record it and poison this unit's outputs so that they cannot pass as results
+        atomicMax(&g_l32_fwd_error, fail);
+        y_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
+        if (sT_ != nullptr) sT_[sbase] = __int_as_float(0x7fc00000);
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {

@@ -371,7 +371,11 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_c
     tc_fence_before();
     __syncthreads();
     const int ab = *abort_word;
-    if (ab && tid == 0) atomicMax(&g_l32_fwdp_error, ab);
+    if (ab && tid == 0) {   // a wait ran out: record it and poison this unit's outputs so that they cannot pass as results
+        atomicMax(&g_l32_fwdp_error, ab);
+        y_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
+        if (sT_ != nullptr) sT_[sbase] = __int_as_float(0x7fc00000);
+    }
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tm0) : "memory");
 }
 

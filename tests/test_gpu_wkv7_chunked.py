@@ -140,8 +140,10 @@ def test_bounded_wait_runs_out_and_the_library_recovers():
     inp = Hh.v7_inputs(1, 64, 2, 64, seed=3)
     good = _run_both(R, inp, 2, True, True)
     _lib.call("rwkvb200_wkv7_test_expire_next_forward")
-    _run_both(R, inp, 2, True, True)
+    bad = _run_both(R, inp, 2, True, True)
     assert L.rwkvb200_device_status() == 11
+    # the units whose wait ran out are marked: their first y element and first sT element are NaN
+    assert torch.isnan(bad["y"].float()).any() and torch.isnan(bad["sT"]).any()
     assert L.rwkvb200_device_status() == 11, "the status word is sticky"
     _lib.call("rwkvb200_device_status_clear")
     assert L.rwkvb200_device_status() == 0
