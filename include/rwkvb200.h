@@ -185,6 +185,20 @@ int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const 
                                    void* gk, void* gv, void* gw, void* gu, float* ds0,
                                    void* scratch, void* stream);
 
+/* Forward split over time (two-level scan): T is cut into `segments` pieces that run at the same time, for
+ * launches with few (batch, head) units.  Replaces the idea of the reference's forward-only
+ * wkv5_bf16/cuda/wkv5_cuda_v3.cu:12-128 (kernel_forward_accumulate_state + kernel_forward<true>), extended to
+ * RWKV-6's per-token decay and to a state in / out.  bf16, head size 64, T/segments a multiple of 16,
+ * 16-byte aligned tensors; `work`: rwkvb200_wkv6_tsplit_bytes(...) bytes of device memory.  Arguments otherwise
+ * as rwkvb200_wkv5_forward / rwkvb200_wkv6state_forward_ex; results equal theirs to rounding. */
+size_t rwkvb200_wkv6_tsplit_bytes(int B, int T, int C, int H, int segments);
+int rwkvb200_wkv5_forward_tsplit(int dtype, int B, int T, int C, int H, int segments, const void* r,
+                                 const void* k, const void* v, const float* w, const void* u, void* y,
+                                 void* work, void* stream);
+int rwkvb200_wkv6state_forward_tsplit(int dtype, int B, int T, int C, int H, int segments, const void* r,
+                                      const void* k, const void* v, const void* w, const void* u,
+                                      const float* s0, void* y, float* sT, void* work, void* stream);
+
 /* ---------------------------------------------------------------------------------
  * RWKV-7 generalised delta rule with soft-clamped decay, bf16 or fp32 activations.
  * One pair of entry points serves the three reference operators:

@@ -21,6 +21,7 @@
 // what the reference kernels hand to their autograd wrappers.
 #include "common.cuh"
 #include "wkv6_chunked.cuh"
+#include "wkv6_tsplit.cuh"
 #include <initializer_list>
 #include <type_traits>
 
@@ -310,6 +311,37 @@ extern "C" int rwkvb200_wkv5_forward(int dtype, int B, int T, int C, int H, cons
     return dtype == RWKVB200_F32
                ? launch_fwd<float, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, as_stream(stream))
                : launch_fwd<bf16, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, as_stream(stream));
+}
+
+// The forward split over time (wkv6_tsplit.cu; the reference's wkv5_bf16/cuda/wkv5_cuda_v3.cu is the same idea):
+// `segments` pieces of T/segments tokens run at the same time.  Tensor-core shapes only (bf16, head size 64,
+// T/segments a multiple of 16, 16-byte aligned tensors).  work: rwkvb200_wkv6_tsplit_bytes(B,T,C,H,segments) bytes.
+extern "C" int rwkvb200_wkv5_forward_tsplit(int dtype, int B, int T, int C, int H, int segments, const void* r,
+                                            const void* k, const void* v, const float* w, const void* u, void* y,
+                                            void* work, void* stream) {
+    if (int e = check_dims("wkv5_forward_tsplit", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(y); RWKV_NOTNULL(work);
+    const int K = segments, N = C / H;
+    RWKV_REQUIRE(K >= 1 && T % K == 0 && (T / K) % 16 == 0, RWKVB200_EINVAL,
+                 "wkv5_forward_tsplit: T = %d is not %d segments of a multiple of 16 tokens", T, K);
+    RWKV_REQUIRE(dtype == RWKVB200_BF16 && chunked_ok<bf16>(T / K, N, {r, k, v, u, y, work}), RWKVB200_EINVAL,
+                 "wkv5_forward_tsplit: needs bf16 tensors, head size 64, 16-byte alignment");
+    cudaStream_t st = as_stream(stream);
+    int* flag = wkv6_chunked_flag(st);
+    if (flag == nullptr || K == 1)   // no flag word left for this stream, or nothing to split: the plain forward
+        return launch_fwd<bf16, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, st);
+    RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA,
+                 "wkv5_forward_tsplit: clearing the device flag failed");
+    float* wk = static_cast<float*>(work);
+    float* start = wk + (size_t)B * K * H * N * N;
+    // 1. every segment from a zero state, states only  2. segment start states  3. every segment with its start state
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 2, u, nullptr, 0, nullptr, wk, nullptr, flag, st)) return e;
+    if (int e = wkv6_tsplit_states(B, T, C, H, K, w, 2, nullptr, wk, nullptr, st)) return e;
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 2, u, start, 2, y, nullptr, nullptr, flag, st)) return e;
+    // a decay too strong for the chunked form: the general-shape kernel redoes the call
+    wkv5_forward_kernel<bf16, 64, false><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w,
+                                                              (const bf16*)u, nullptr, nullptr, (bf16*)y, flag);
+    return check_launch("wkv5_forward_tsplit");
 }
 
 extern "C" int rwkvb200_wkv5_backward(int dtype, int B, int T, int C, int H, const void* r, const void* k,

@@ -23,6 +23,7 @@
 #include <atomic>
 #include "common.cuh"
 #include "wkv6_chunked.cuh"
+#include "wkv6_tsplit.cuh"
 #include <initializer_list>
 #include <type_traits>
 
@@ -444,6 +445,42 @@ extern "C" int rwkvb200_wkv6state_forward_ex(int dtype, int B, int T, int C, int
     return dtype == RWKVB200_F32
                ? launch_fwd<float>(B, T, C, H, r, k, v, w, 1, u, s0, sk, y, sT, as_stream(stream), "wkv6state_forward_ex")
                : launch_fwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, sk, y, sT, as_stream(stream), "wkv6state_forward_ex");
+}
+
+// The forward split over time (wkv6_tsplit.cu): `segments` pieces of T/segments tokens run at the same time.
+// Tensor-core shapes only (bf16, head size 64, T/segments a multiple of 16, 16-byte aligned tensors); a decay too
+// strong for the chunked form makes the general-shape kernel redo the whole call, as in the unsplit forward.
+extern "C" size_t rwkvb200_wkv6_tsplit_bytes(int B, int T, int C, int H, int segments) {
+    (void)T;
+    return (B > 0 && C > 0 && H > 0 && segments > 0) ? wkv6_tsplit_bytes(B, C, H, segments) : 0;
+}
+
+extern "C" int rwkvb200_wkv6state_forward_tsplit(int dtype, int B, int T, int C, int H, int segments, const void* r,
+                                                 const void* k, const void* v, const void* w, const void* u,
+                                                 const float* s0, void* y, float* sT, void* work, void* stream) {
+    if (int e = check_dims("wkv6state_forward_tsplit", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(y); RWKV_NOTNULL(work);
+    const int K = segments, N = C / H;
+    RWKV_REQUIRE(K >= 1 && T % K == 0 && (T / K) % 16 == 0, RWKVB200_EINVAL,
+                 "wkv6state_forward_tsplit: T = %d is not %d segments of a multiple of 16 tokens", T, K);
+    RWKV_REQUIRE(dtype == RWKVB200_BF16 && chunked_ok<bf16>(T / K, N, {r, k, v, w, u, s0, y, sT, work}), RWKVB200_EINVAL,
+                 "wkv6state_forward_tsplit: needs bf16 tensors, head size 64, 16-byte alignment");
+    cudaStream_t st = as_stream(stream);
+    int* flag = wkv6_chunked_flag(st);
+    if (flag == nullptr || K == 1)   // no flag word left for this stream, or nothing to split: the plain forward
+        return launch_fwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, s0 ? kF32 : kNone, y, sT, st, "wkv6state_forward_tsplit");
+    RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA,
+                 "wkv6state_forward_tsplit: clearing the device flag failed");
+    float* wk = static_cast<float*>(work);
+    float* start = wk + (size_t)B * K * H * N * N;
+    // 1. every segment from a zero state, states only  2. segment start states  3. every segment with its start state
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 1, u, nullptr, kNone, nullptr, wk, nullptr, flag, st)) return e;
+    if (int e = wkv6_tsplit_states(B, T, C, H, K, w, 1, s0, wk, sT, st)) return e;
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 1, u, start, kF32, y, nullptr, nullptr, flag, st)) return e;
+    // a chunk whose decay is too strong for the chunked form: the general-shape kernel redoes the call
+    wkv6_forward_kernel<bf16, 64><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, 1,
+                                                       (const bf16*)u, s0, s0 ? kF32 : kNone, (bf16*)y, sT, flag);
+    return check_launch("wkv6state_forward_tsplit");
 }
 
 extern "C" int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const void* r, const void* k,

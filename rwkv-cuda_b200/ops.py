@@ -240,6 +240,41 @@ def wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT):
              _ptr(s0, "s0", f), _ptr(y, "y", d), _ptr(sT, "sT", f), _stream(r))
 
 
+def tsplit_segments(B, T, H, device):
+    """How many time segments the split forward should use for this launch: enough to fill the four thread
+    blocks that an SM holds, at least 256 tokens per segment, whole 16-token chunks; 1 when the launch fills
+    the GPU by itself (measured for one sequence of 64 heads, T 4096: 0.46 ms unsplit, 0.44 / 0.30 / 0.27 /
+    0.32 ms with 2 / 4 / 8 / 16 segments)."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    k = max(1, min(4 * sms // max(1, B * H), T // 256))
+    while k > 1 and (T % k != 0 or (T // k) % 16 != 0):
+        k -= 1
+    return k
+
+
+def wkv5_forward_tsplit(B, T, C, H, r, k, v, w, u, y, segments=None):
+    """RWKV-5 forward split over time (few (batch, head) units: the segments run at the same time)."""
+    d = r.dtype
+    for t, n, name in ((r, B * T * C, "r"), (k, B * T * C, "k"), (v, B * T * C, "v"), (w, C, "w"), (u, C, "u"),
+                       (y, B * T * C, "y")):
+        _numel(t, n, name)
+    with _dev(r, "r"):
+        K = segments or tsplit_segments(B, T, H, r.device)
+        wk = scratch(_lib.lib().rwkvb200_wkv6_tsplit_bytes(B, T, C, H, K), r.device)
+        call("rwkvb200_wkv5_forward_tsplit", _dt(r, "r"), B, T, C, H, K, *_ptrs(d, r=r, k=k, v=v),
+             _ptr(w, "w", torch.float32), _ptr(u, "u", d), _ptr(y, "y", d), wk.data_ptr(), _stream(r))
+
+
+def wkv6state_forward_tsplit(B, T, C, H, r, k, v, w, u, s0, y, sT, segments=None):
+    """RWKV-6 forward with fp32 state in / out, split over time."""
+    d, f = r.dtype, torch.float32
+    with _dev(r, "r"):
+        K = segments or tsplit_segments(B, T, H, r.device)
+        wk = scratch(_lib.lib().rwkvb200_wkv6_tsplit_bytes(B, T, C, H, K), r.device)
+        call("rwkvb200_wkv6state_forward_tsplit", _dt(r, "r"), B, T, C, H, K, *_ptrs(d, r=r, k=k, v=v, w=w, u=u),
+             _ptr(s0, "s0", f), _ptr(y, "y", d), _ptr(sT, "sT", f), wk.data_ptr(), _stream(r))
+
+
 def wkv6state_backward_ex(B, T, C, H, r, k, v, w, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0):
     d, f = r.dtype, torch.float32
     with _dev(r, "r"):

@@ -1,0 +1,145 @@
+"""GPU: the forward split over time (two-level scan) for RWKV-5 and RWKV-6 with state, against the fp64
+oracle and against the unsplit forward; the reference's counterpart is the forward-only
+wkv5_bf16/cuda/wkv5_cuda_v3.cu (static decay, no state)."""
+import pytest
+import torch
+
+from oracle import wkv_oracle as O
+from tests import helpers as Hh
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def R():
+    import rwkv_cuda_b200 as R
+    return R
+
+
+def _v6_inputs(B, T, H, N, seed, shift=-3.0):
+    g = Hh.gen(seed)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u = Hh.randn(g, B, T, C) + shift, Hh.rand(g, H, N, lo=-1, hi=1)
+    s0 = 0.1 * Hh.randn(g, B, H, N, N)
+    return r, k, v, w_raw, u, s0
+
+
+@pytest.mark.parametrize("B,T,H,K", [(1, 1024, 2, 4), (2, 512, 3, 2), (1, 256, 1, 8), (1, 96, 2, 3)])
+def test_rwkv6_state_forward_split_over_time(R, B, T, H, K):
+    N = 64
+    C = H * N
+    r, k, v, w_raw, u, s0 = _v6_inputs(B, T, H, N, seed=11)
+    xs = [x.to(BF).double() for x in (r, k, v, w_raw, u)]
+    yo, sTo = O.wkv6(*xs, H, s0=s0.double(), return_state=True)
+    rd, kd, vd, wd, ud = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, w_raw, u))
+    s0d = s0.to(DEV)
+    y, sT = torch.full((B, T, C), float("nan"), dtype=BF, device=DEV), torch.full((B, H, N, N), float("nan"), device=DEV)
+    R.ops.wkv6state_forward_tsplit(B, T, C, H, rd, kd, vd, wd, ud, s0d, y, sT, segments=K)
+    y1, sT1 = torch.empty_like(y), torch.empty_like(sT)
+    R.ops.wkv6state_forward_ex(B, T, C, H, rd, kd, vd, wd, ud, s0d, y1, sT1)
+    torch.cuda.synchronize()
+    Hh.assert_close(y, yo, Hh.TOL_BF16, "y (split) against the oracle")
+    Hh.assert_close(sT, sTo, Hh.TOL_BF16, "sT (split) against the oracle")
+    # against the unsplit kernel: the same products inside a segment, start states combined in another order
+    Hh.assert_close(y, y1.double().cpu(), Hh.TOL_BF16, "y split against unsplit")
+    Hh.assert_close(sT, sT1.double().cpu(), Hh.TOL_BF16,
+                    "sT split against unsplit")
+
+
+def test_rwkv6_split_without_a_state(R):
+    B, T, H, N, K = 1, 512, 2, 64, 4
+    C = H * N
+    r, k, v, w_raw, u, _ = _v6_inputs(B, T, H, N, seed=12)
+    xs = [x.to(BF).double() for x in (r, k, v, w_raw, u)]
+    yo = O.wkv6(*xs, H)
+    rd, kd, vd, wd, ud = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, w_raw, u))
+    y = torch.full((B, T, C), float("nan"), dtype=BF, device=DEV)
+    R.ops.wkv6state_forward_tsplit(B, T, C, H, rd, kd, vd, wd, ud, None, y, None, segments=K)
+    torch.cuda.synchronize()
+    Hh.assert_close(y, yo, Hh.TOL_BF16, "y (split, zero start state)")
+
+
+@pytest.mark.parametrize("B,T,H,K", [(1, 1024, 2, 4), (2, 256, 3, 2)])
+def test_rwkv5_forward_split_over_time(R, B, T, H, K):
+    N = 64
+    C = H * N
+    g = Hh.gen(21)
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u = Hh.rand(g, H, N, lo=-6, hi=-1), Hh.rand(g, H, N, lo=-1, hi=1)
+    xs = [x.to(BF).double() for x in (r, k, v, w_raw, u)]
+    yo = O.wkv5(*xs, H)
+    rd, kd, vd, ud = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, u))
+    eew = torch.exp(-torch.exp(w_raw.to(BF).float())).to(DEV).contiguous()
+    y = torch.full((B, T, C), float("nan"), dtype=BF, device=DEV)
+    R.ops.wkv5_forward_tsplit(B, T, C, H, rd, kd, vd, eew, ud, y, segments=K)
+    y1 = torch.empty_like(y)
+    R.ops.wkv5_forward(B, T, C, H, rd, kd, vd, eew, ud, y1)
+    torch.cuda.synchronize()
+    Hh.assert_close(y, yo, Hh.TOL_BF16, "y (split) against the oracle")
+    Hh.assert_close(y, y1.double().cpu(), Hh.TOL_BF16, "y split against unsplit")
+
+
+def test_split_with_a_decay_too_strong_for_the_chunked_form(R):
+    """Log-decays below -5 per token: the chunked kernels raise their flag and the general-shape kernel redoes
+    the whole call, split or not."""
+    B, T, H, N, K = 1, 128, 2, 64, 2
+    C = H * N
+    r, k, v, w_raw, u, s0 = _v6_inputs(B, T, H, N, seed=13, shift=2.0)
+    xs = [x.to(BF).double() for x in (r, k, v, w_raw, u)]
+    yo, sTo = O.wkv6(*xs, H, s0=s0.double(), return_state=True)
+    rd, kd, vd, wd, ud = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, w_raw, u))
+    y, sT = torch.full((B, T, C), float("nan"), dtype=BF, device=DEV), torch.full((B, H, N, N), float("nan"), device=DEV)
+    R.ops.wkv6state_forward_tsplit(B, T, C, H, rd, kd, vd, wd, ud, s0.to(DEV), y, sT, segments=K)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all() and torch.isfinite(sT).all()
+    Hh.assert_close(y, yo, Hh.TOL_BF16, "y (split, strong decay)")
+    Hh.assert_close(sT, sTo, Hh.TOL_BF16, "sT (split, strong decay)")
+
+
+def test_split_rejects_segments_that_are_not_whole_chunks(R):
+    B, T, H, N = 1, 96, 1, 64
+    C = H * N
+    z = torch.zeros(B, T, C, dtype=BF, device=DEV)
+    u = torch.zeros(H, N, dtype=BF, device=DEV)
+    with pytest.raises(Exception):
+        R.ops.wkv6state_forward_tsplit(B, T, C, H, z, z, z, z, u, None, torch.empty_like(z), None, segments=4)   # 24 tokens
+
+
+def test_split_pays_for_a_single_sequence(R):
+    """One sequence of 64 heads on 148 SMs: the split forward is faster than the unsplit one (measured 1.7x with
+    the 8 segments that are chosen automatically); prints the times."""
+    B, T, H, N = 1, 4096, 64, 64
+    C = H * N
+    g = torch.Generator(device=DEV)
+    g.manual_seed(5)
+    mk = lambda sc=0.5: (sc * torch.randn(B, T, C, generator=g, device=DEV)).to(BF)
+    r, k, v = mk(), mk(), mk()
+    w = (torch.randn(B, T, C, generator=g, device=DEV) - 3.0).to(BF)
+    u = (torch.rand(H, N, generator=g, device=DEV) * 2 - 1).to(BF)
+    s0 = 0.1 * torch.randn(B, H, N, N, generator=g, device=DEV)
+    y, sT = torch.empty(B, T, C, dtype=BF, device=DEV), torch.empty_like(s0)
+    K = R.ops.tsplit_segments(B, T, H, torch.device(DEV))
+    assert K >= 2
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 10
+
+    t_plain = timed(lambda: R.ops.wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT))
+    for kk in (2, 4, 8, 16):
+        tk = timed(lambda: R.ops.wkv6state_forward_tsplit(B, T, C, H, r, k, v, w, u, s0, y, sT, segments=kk))
+        print(f"RWKV-6 forward B1 T4096 H64: {kk} segments {tk:.3f} ms")
+    t_split = timed(lambda: R.ops.wkv6state_forward_tsplit(B, T, C, H, r, k, v, w, u, s0, y, sT))
+    print(f"RWKV-6 forward B1 T4096 H64: unsplit {t_plain:.3f} ms, split into {K} segments (automatic) {t_split:.3f} ms")
+    assert t_split < 0.8 * t_plain
