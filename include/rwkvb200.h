@@ -109,6 +109,13 @@ int rwkvb200_wkv5_backward_ws(int dtype, int B, int T, int C, int H, const void*
                               const void* v, const float* w, const float* ww, const void* u,
                               const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
                               void* scratch, void* stream);
+/* The same with, in addition, the (B,C) partials of gw and gu unrounded in fp32: summed over the batch with
+ * rwkvb200_reduce_batch_partials they are the parameter gradients without the bf16 round trip of the reference
+ * harness (wkv5_bf16/run.py:83-87). */
+int rwkvb200_wkv5_backward_ws32(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                const void* v, const float* w, const float* ww, const void* u,
+                                const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                                float* gw32, float* gu32, void* scratch, void* stream);
 
 /* ---------------------------------------------------------------------------------
  * RWKV-5a WKV (decay w1[j]*w2[i], bonus u1[j]+u2[i]), fp32 or bf16 activations.

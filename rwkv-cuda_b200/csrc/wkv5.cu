@@ -257,11 +257,20 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
     return check_launch(DUAL ? "wkv5a_forward" : "wkv5_forward");
 }
 
+// fp32 copies of the (B,C) partials; only_if: run only when that device flag is set (NULL: always)
+template <typename E>
+__global__ void widen_partials_kernel(int n, const E* __restrict__ gw, const E* __restrict__ gu, float* __restrict__ gw32,
+                                      float* __restrict__ gu32, const int* __restrict__ only_if) {
+    if (only_if != nullptr && *only_if == 0) return;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { gw32[i] = to_f(gw[i]); gu32[i] = to_f(gu[i]); }
+}
+
 template <typename E, bool DUAL>
 int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const void* v, const float* w1,
                const float* ww1, const void* u1, const float* w2, const float* ww2, const void* u2, const void* gy,
                void* gr, void* gk, void* gv, void* gw1, void* gu1, void* gw2, void* gu2, cudaStream_t st,
-               void* scratch = nullptr) {
+               void* scratch = nullptr, float* gw32 = nullptr, float* gu32 = nullptr) {
     const int N = C / H;
     const int* only_if = nullptr;
     if (!DUAL && scratch != nullptr && chunked_ok<E>(T, N, {r, k, v, u1, gy, gr, gk, gv, gw1, gu1, scratch})) {
@@ -272,7 +281,7 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
             RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_backward: clearing the device flag failed");
             float* ck = static_cast<float*>(scratch);
             if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
-            if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st))
+            if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st, gw32, gu32))
                 return e;
             only_if = flag;
         }
@@ -287,6 +296,11 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         default: RWKV_GO(128); break;
     }
 #undef RWKV_GO
+    if (gw32 != nullptr && gu32 != nullptr) {
+        // the general-shape kernel has the (B,C) partials in the activation type only: where it ran (it was the
+        // only kernel, or the chunked one raised its flag) the fp32 copies are made from those
+        widen_partials_kernel<E><<<(B * C + 255) / 256, 256, 0, st>>>(B * C, (const E*)gw1, (const E*)gu1, gw32, gu32, only_if);
+    }
     return check_launch(DUAL ? "wkv5a_backward" : "wkv5_backward");
 }
 
@@ -375,6 +389,24 @@ extern "C" int rwkvb200_wkv5_backward_ws(int dtype, int B, int T, int C, int H, 
                                           gw, gu, nullptr, nullptr, as_stream(stream), scratch)
                : launch_bwd<bf16, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
                                          gw, gu, nullptr, nullptr, as_stream(stream), scratch);
+}
+
+// As rwkvb200_wkv5_backward_ws, and in addition the (B,C) partials of gw and gu unrounded in fp32 (gw32, gu32):
+// summed over the batch with rwkvb200_reduce_batch_partials they give the parameter gradients without the
+// bf16 round trip of the reference harness (wkv5_bf16/run.py:83-87).
+extern "C" int rwkvb200_wkv5_backward_ws32(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                           const void* v, const float* w, const float* ww, const void* u,
+                                           const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                                           float* gw32, float* gu32, void* scratch, void* stream) {
+    if (int e = check_dims("wkv5_backward_ws32", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(ww); RWKV_NOTNULL(u);
+    RWKV_NOTNULL(gy); RWKV_NOTNULL(gr); RWKV_NOTNULL(gk); RWKV_NOTNULL(gv); RWKV_NOTNULL(gw); RWKV_NOTNULL(gu);
+    RWKV_NOTNULL(gw32); RWKV_NOTNULL(gu32); RWKV_NOTNULL(scratch);
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
+                                          gw, gu, nullptr, nullptr, as_stream(stream), scratch, gw32, gu32)
+               : launch_bwd<bf16, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv,
+                                         gw, gu, nullptr, nullptr, as_stream(stream), scratch, gw32, gu32);
 }
 
 extern "C" int rwkvb200_wkv5a_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,

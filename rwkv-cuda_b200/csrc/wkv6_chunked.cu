@@ -283,7 +283,8 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                       const bf16* __restrict__ v_, const void* __restrict__ w_, const bf16* __restrict__ u_,
                       const bf16* __restrict__ gy_, const float* __restrict__ dsT_, const float* __restrict__ ck_,
                       bf16* __restrict__ gr_, bf16* __restrict__ gk_, bf16* __restrict__ gv_, bf16* __restrict__ gw_,
-                      bf16* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind) {
+                      bf16* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind, float* __restrict__ gw32_,
+                      float* __restrict__ gu32_) {
     constexpr bool gw_reduce = WMODE >= 2;   // a static decay has one gradient per channel and batch row
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* sm = reinterpret_cast<float*>(smem_raw);
@@ -594,10 +595,12 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         gu_acc[h2] += __shfl_xor_sync(0xffffffffu, gu_acc[h2], 1);
         gu_acc[h2] += __shfl_xor_sync(0xffffffffu, gu_acc[h2], 2);
         if (t == 0) gu_[(i64)bb * C + hh * N + row0 + 2 * g + h2] = __float2bfloat16_rn(gu_acc[h2]);
+        if (t == 0 && gu32_ != nullptr) gu32_[(i64)bb * C + hh * N + row0 + 2 * g + h2] = gu_acc[h2];   // unrounded
         if (gw_reduce) {
             gw_acc[h2] += __shfl_xor_sync(0xffffffffu, gw_acc[h2], 1);
             gw_acc[h2] += __shfl_xor_sync(0xffffffffu, gw_acc[h2], 2);
             if (t == 0) gw_[(i64)bb * C + hh * N + row0 + 2 * g + h2] = __float2bfloat16_rn(gw_acc[h2]);
+            if (t == 0 && gw32_ != nullptr) gw32_[(i64)bb * C + hh * N + row0 + 2 * g + h2] = gw_acc[h2];
         }
     }
     if (ds0_kind != 0) {
@@ -674,7 +677,8 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
 
 int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                           const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
-                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st) {
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st, float* gw32,
+                          float* gu32) {
     using namespace v6c;
     static_assert(BSmem::kBytes <= 113 * 1024, "backward shared memory must allow 2 CTAs per SM");
     RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_backward(chunked): decay mode %d", w_mode);
@@ -687,7 +691,7 @@ int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, con
         wkv6c_backward_kernel<M><<<grid, NT, BSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, \
                                                                   (const bf16*)u, (const bf16*)gy, dsT, ck, (bf16*)gr,  \
                                                                   (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0,      \
-                                                                  ds0_kind);                                            \
+                                                                  ds0_kind, gw32, gu32);                                \
     } while (0)
     switch (w_mode) {
         case 0: RWKV_GO(0); break;

@@ -17,7 +17,8 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
 // (fp32, (B,H,T/16,N,N)).  ds0_kind as s0_kind (0: no state gradient out).  gu is per batch: (B,C).
 int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                           const void* u, const void* gy, const float* dsT, const float* ck, void* gr, void* gk,
-                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st);
+                          void* gv, void* gw, void* gu, void* ds0, int ds0_kind, cudaStream_t st,
+                          float* gw32 = nullptr, float* gu32 = nullptr);   // optional unrounded (B,C) partials of gu (and of gw for a static decay)
 // With a static decay (w_mode 2, 3) gw is summed over time into (B,C) instead of written per token.
 
 // one slot of a ring of device flags for `unsafe` (clear it in the stream before the forward)

@@ -76,9 +76,15 @@ class WKV_5(torch.autograd.Function):
             r, k, v, eew, ew, u = ctx.saved_tensors
             gr, gk, gv = (torch.empty((B, T, C), device=gy.device, dtype=r.dtype) for _ in range(3))
             gw, gu = (torch.empty((B, C), device=gy.device, dtype=r.dtype) for _ in range(2))
-            ops.wkv5_backward(B, T, C, H, r, k, v, eew, ew, u, gy.contiguous(), gr, gk, gv, gw, gu)
+            # the harness sums bf16 (B,C) partials in bf16 (wkv5_bf16/run.py:83-87); here the unrounded fp32
+            # partials are summed in fp32 on the device and rounded once
+            gw32, gu32 = (torch.empty((B, C), device=gy.device, dtype=torch.float32) for _ in range(2))
+            ops.wkv5_backward(B, T, C, H, r, k, v, eew, ew, u, gy.contiguous(), gr, gk, gv, gw, gu, gw32, gu32)
+            sums = torch.empty((2, C), device=gy.device, dtype=torch.float32)
+            ops.reduce_batch_partials(gw32, sums[0])
+            ops.reduce_batch_partials(gu32, sums[1])
             shape = u.shape
-            return (None, None, None, None, gr, gk, gv, torch.sum(gw, 0).view(shape), torch.sum(gu, 0).view(shape))
+            return (None, None, None, None, gr, gk, gv, sums[0].to(u.dtype).view(shape), sums[1].to(u.dtype).view(shape))
 
 
 class WKV_5A(torch.autograd.Function):

@@ -121,7 +121,9 @@ def wkv5_forward(B, T, C, H, r, k, v, w, u, y):
              _ptr(u, "u", d), _ptr(y, "y", d), _stream(r))
 
 
-def wkv5_backward(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu):
+def wkv5_backward(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu, gw32=None, gu32=None):
+    """gw32, gu32 (optional, both or none): fp32 (B,C) tensors that receive the unrounded partials of gw and gu
+    (reduce them with reduce_batch_partials: no bf16 round trip on the parameter gradients)."""
     d = r.dtype
     for t, n, name in ((r, B * T * C, "r"), (k, B * T * C, "k"), (v, B * T * C, "v"), (w, C, "w"), (ww, C, "ww"),
                        (u, C, "u"), (gy, B * T * C, "gy"), (gr, B * T * C, "gr"), (gk, B * T * C, "gk"),
@@ -129,9 +131,17 @@ def wkv5_backward(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu):
         _numel(t, n, name)
     with _dev(r, "r"):
         sc = scratch(_lib.lib().rwkvb200_wkv5_scratch_bytes(B, T, C), r.device)
-        call("rwkvb200_wkv5_backward_ws", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
-             _ptr(w, "w", torch.float32), _ptr(ww, "ww", torch.float32),
-             *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), sc.data_ptr(), _stream(r))
+        if gw32 is None and gu32 is None:
+            call("rwkvb200_wkv5_backward_ws", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
+                 _ptr(w, "w", torch.float32), _ptr(ww, "ww", torch.float32),
+                 *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), sc.data_ptr(), _stream(r))
+        else:
+            _numel(gw32, B * C, "gw32")
+            _numel(gu32, B * C, "gu32")
+            call("rwkvb200_wkv5_backward_ws32", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
+                 _ptr(w, "w", torch.float32), _ptr(ww, "ww", torch.float32),
+                 *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), _ptr(gw32, "gw32", torch.float32),
+                 _ptr(gu32, "gu32", torch.float32), sc.data_ptr(), _stream(r))
 
 
 def reduce_batch_partials(partial, out):

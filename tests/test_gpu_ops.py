@@ -176,6 +176,38 @@ def test_wkv5_strong_decay_falls_back(R):
         Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv5 strong decay {name}")
 
 
+@pytest.mark.parametrize("dtype,B,T,H,N,hi", [(torch.bfloat16, 4, 256, 2, 64, -1.0),    # chunked kernels
+                                                 (torch.bfloat16, 4, 64, 2, 64, 2.5),       # strong decay: general-shape kernel redoes it
+                                                 (torch.bfloat16, 3, 40, 2, 32, -1.0),      # general-shape kernel only
+                                                 (torch.float32, 2, 48, 2, 64, -1.0)])
+def test_wkv5_parameter_gradients_without_the_bf16_round_trip(R, dtype, B, T, H, N, hi):
+    """The fp32 (B,C) partials of gw, gu summed in fp32: at least as close to the oracle as the sum of the
+    partials in the activation type, on every kernel path."""
+    g = Hh.gen(9)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.rand(g, H, N, lo=-6 if hi < 0 else -1, hi=hi), Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv5(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    rd, kd, vd, ud, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, u, gy))
+    ew = -torch.exp(w_raw.to(dtype).float()).to(DEV).contiguous()
+    eew = torch.exp(ew).contiguous()
+    gr, gk, gv = (sentinel(B, T, C, dtype=dtype) for _ in range(3))
+    gw, gu = sentinel(B, C, dtype=dtype), sentinel(B, C, dtype=dtype)
+    gw32, gu32 = sentinel(B, C), sentinel(B, C)
+    R.ops.wkv5_backward(B, T, C, H, rd, kd, vd, eew, ew, ud, gd, gr, gk, gv, gw, gu, gw32, gu32)
+    sums = torch.empty(2, C, device=DEV)
+    R.ops.reduce_batch_partials(gw32, sums[0])
+    R.ops.reduce_batch_partials(gu32, sums[1])
+    torch.cuda.synchronize()
+    for name, got32, part, want in (("gw", sums[0], gw, xs[3].grad), ("gu", sums[1], gu, xs[4].grad)):
+        Hh.assert_close(got32, want, Hh.tol_for(dtype), f"wkv5 {name} from fp32 partials")
+        e32 = O.err_ratio(want.reshape(-1), got32.double().cpu())
+        e16 = O.err_ratio(want.reshape(-1), part.float().sum(0).double().cpu())
+        assert e32 <= e16 * 1.05 + 1e-7, (name, e32, e16)
+
+
 def run_wkv5a(R, dtype, H, r, k, v, w1, u1, w2, u2, gy):
     B, T, C = r.shape
     rd, kd, vd, u1d, u2d, gd = (x.to(dtype).to(DEV).contiguous() for x in (r, k, v, u1, u2, gy))
