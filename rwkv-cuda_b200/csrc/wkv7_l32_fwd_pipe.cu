@@ -13,7 +13,7 @@
 // warps synchronise on a named barrier.  One thread block per SM (220 KB of shared memory, 256 columns of
 // tensor memory).  Measured per chunk: loader 3.7 k cycles, matrix group 3.1 k, chain group 3.4 k, against
 // 7.2 k for one thread block of wkv7_l32_fwd.cu alone and 11 k with three on an SM (3.7 k per chunk and SM):
-// B = 16, T = 4096 1.78 ms against 1.94 ms, B = 2 0.27 ms against 0.48 ms.  What did not help: the 192 rows of
+// B = 16, T = 4096 1.70 ms against 1.94 ms, B = 2 0.27 ms against 0.48 ms.  What did not help: the 192 rows of
 // a chunk as untiled bulk copies of 128 bytes (the copy engine takes about 60 cycles per copy: 13 k cycles per
 // chunk), the chunk after next requested with plain loads into a second register set (the 48 loads take
 // 1.7 k cycles to issue), eight loader warps (preparation 3.9 k instead of 3.3 k), the six tiles issued by
