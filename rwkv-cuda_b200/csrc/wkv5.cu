@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(NMAX) wkv5_forward_kernel(int T, int C, int H,
                                                            const float* __restrict__ w1_, const E* __restrict__ u1_,
                                                            const float* __restrict__ w2_, const E* __restrict__ u2_,
                                                            E* __restrict__ y_, const int* __restrict__ only_if_) {
-    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernel's result stands
+    if (only_if_ != nullptr && only_if_[blockIdx.x & (kChunkedFlagUnits - 1)] == 0) return;   // fallback launch: the chunked kernel's result stands for this unit
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks;
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(NMAX) wkv5_backward_kernel(
     const float* __restrict__ w2_, const float* __restrict__ ww2_, const E* __restrict__ u2_,
     const E* __restrict__ gy_, E* __restrict__ gr_, E* __restrict__ gk_, E* __restrict__ gv_, E* __restrict__ gw1_,
     E* __restrict__ gu1_, E* __restrict__ gw2_, E* __restrict__ gu2_, const int* __restrict__ only_if_) {
-    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernels' result stands
+    if (only_if_ != nullptr && only_if_[blockIdx.x & (kChunkedFlagUnits - 1)] == 0) return;   // fallback launch: the chunked kernels' result stands for this unit
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks, vs, gs;
@@ -240,7 +240,7 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
         // runs first, the general-shape kernel below only if the decay is too strong for the chunked form
         int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
         if (flag != nullptr) {
-            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_forward: clearing the device flag failed");
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_forward: clearing the device flag failed");
             if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w1, 2, u1, nullptr, 0, y, nullptr, nullptr, flag, st)) return e;
             only_if = flag;
         }
@@ -259,11 +259,13 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
 
 // fp32 copies of the (B,C) partials; only_if: run only when that device flag is set (NULL: always)
 template <typename E>
-__global__ void widen_partials_kernel(int n, const E* __restrict__ gw, const E* __restrict__ gu, float* __restrict__ gw32,
-                                      float* __restrict__ gu32, const int* __restrict__ only_if) {
-    if (only_if != nullptr && *only_if == 0) return;
+__global__ void widen_partials_kernel(int n, int C, int N, const E* __restrict__ gw, const E* __restrict__ gu,
+                                      float* __restrict__ gw32, float* __restrict__ gu32, const int* __restrict__ only_if) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) { gw32[i] = to_f(gw[i]); gu32[i] = to_f(gu[i]); }
+    if (i >= n) return;
+    const int unit = (i / C) * (C / N) + (i % C) / N;   // (batch, head) of this element
+    if (only_if != nullptr && only_if[unit & (kChunkedFlagUnits - 1)] == 0) return;
+    gw32[i] = to_f(gw[i]); gu32[i] = to_f(gu[i]);
 }
 
 template <typename E, bool DUAL>
@@ -278,7 +280,7 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         // general-shape kernel only if the decay is too strong for the chunked form
         int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
         if (flag != nullptr) {
-            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_backward: clearing the device flag failed");
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_backward: clearing the device flag failed");
             float* ck = static_cast<float*>(scratch);
             if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
             if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st, gw32, gu32))
@@ -299,7 +301,7 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
     if (gw32 != nullptr && gu32 != nullptr) {
         // the general-shape kernel has the (B,C) partials in the activation type only: where it ran (it was the
         // only kernel, or the chunked one raised its flag) the fp32 copies are made from those
-        widen_partials_kernel<E><<<(B * C + 255) / 256, 256, 0, st>>>(B * C, (const E*)gw1, (const E*)gu1, gw32, gu32, only_if);
+        widen_partials_kernel<E><<<(B * C + 255) / 256, 256, 0, st>>>(B * C, C, N, (const E*)gw1, (const E*)gu1, gw32, gu32, only_if);
     }
     return check_launch(DUAL ? "wkv5a_backward" : "wkv5_backward");
 }
@@ -344,14 +346,14 @@ extern "C" int rwkvb200_wkv5_forward_tsplit(int dtype, int B, int T, int C, int 
     int* flag = wkv6_chunked_flag(st);
     if (flag == nullptr || K == 1)   // no flag word left for this stream, or nothing to split: the plain forward
         return launch_fwd<bf16, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, st);
-    RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA,
+    RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA,
                  "wkv5_forward_tsplit: clearing the device flag failed");
     float* wk = static_cast<float*>(work);
     float* start = wk + (size_t)B * K * H * N * N;
     // 1. every segment from a zero state, states only  2. segment start states  3. every segment with its start state
-    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 2, u, nullptr, 0, nullptr, wk, nullptr, flag, st)) return e;
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 2, u, nullptr, 0, nullptr, wk, nullptr, flag, st, K)) return e;
     if (int e = wkv6_tsplit_states(B, T, C, H, K, w, 2, nullptr, wk, nullptr, st)) return e;
-    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 2, u, start, 2, y, nullptr, nullptr, flag, st)) return e;
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 2, u, start, 2, y, nullptr, nullptr, flag, st, K)) return e;
     // a decay too strong for the chunked form: the general-shape kernel redoes the call
     wkv5_forward_kernel<bf16, 64, false><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w,
                                                               (const bf16*)u, nullptr, nullptr, (bf16*)y, flag);

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(NMAX) wkv6_forward_kernel(int T, int C, int H,
                                                            const E* __restrict__ u_, const void* __restrict__ s0_,
                                                            int s0_kind, E* __restrict__ y_, float* __restrict__ sT_,
                                                            const int* __restrict__ only_if_) {
-    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernel's result stands
+    if (only_if_ != nullptr && only_if_[blockIdx.x & (kChunkedFlagUnits - 1)] == 0) return;   // fallback launch: the chunked kernel's result stands for this unit
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks, ds;
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(NMAX) wkv6_backward_kernel(
     const E* __restrict__ gy_, const float* __restrict__ dsT_, E* __restrict__ gr_, E* __restrict__ gk_,
     E* __restrict__ gv_, E* __restrict__ gw_, E* __restrict__ gu_, void* __restrict__ ds0_, int ds0_kind,
     float* __restrict__ scratch_, const int* __restrict__ only_if_) {
-    if (only_if_ != nullptr && *only_if_ == 0) return;   // fallback launch: the chunked kernels' result stands
+    if (only_if_ != nullptr && only_if_[blockIdx.x & (kChunkedFlagUnits - 1)] == 0) return;   // fallback launch: the chunked kernels' result stands for this unit
     const int b = blockIdx.x / H, h = blockIdx.x - b * H, i = threadIdx.x;
     const bool live = i < N;
     __shared__ Stage<NMAX> rs, ks, vs, gs, ds;
@@ -263,7 +263,7 @@ int launch_fwd(int B, int T, int C, int H, const void* r, const void* k, const v
         // chunk whose decay is too strong for the chunked form
         int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
         if (flag != nullptr) {
-            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
             if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, y, sT, nullptr, flag, st)) return e;
             only_if = flag;
         }
@@ -293,7 +293,7 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         // was too strong for the chunked form (it reuses the front of the same scratch buffer)
         int* flag = wkv6_chunked_flag(st);   // NULL: every slot is taken, the general-shape kernel runs alone
         if (flag != nullptr) {
-            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
+            RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
             float* ck = static_cast<float*>(scratch);
             if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
             if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
@@ -469,14 +469,14 @@ extern "C" int rwkvb200_wkv6state_forward_tsplit(int dtype, int B, int T, int C,
     int* flag = wkv6_chunked_flag(st);
     if (flag == nullptr || K == 1)   // no flag word left for this stream, or nothing to split: the plain forward
         return launch_fwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, s0 ? kF32 : kNone, y, sT, st, "wkv6state_forward_tsplit");
-    RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int), st) == cudaSuccess, RWKVB200_ECUDA,
+    RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA,
                  "wkv6state_forward_tsplit: clearing the device flag failed");
     float* wk = static_cast<float*>(work);
     float* start = wk + (size_t)B * K * H * N * N;
     // 1. every segment from a zero state, states only  2. segment start states  3. every segment with its start state
-    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 1, u, nullptr, kNone, nullptr, wk, nullptr, flag, st)) return e;
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 1, u, nullptr, kNone, nullptr, wk, nullptr, flag, st, K)) return e;
     if (int e = wkv6_tsplit_states(B, T, C, H, K, w, 1, s0, wk, sT, st)) return e;
-    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 1, u, start, kF32, y, nullptr, nullptr, flag, st)) return e;
+    if (int e = wkv6_chunked_forward(B * K, T / K, H, r, k, v, w, 1, u, start, kF32, y, nullptr, nullptr, flag, st, K)) return e;
     // a chunk whose decay is too strong for the chunked form: the general-shape kernel redoes the call
     wkv6_forward_kernel<bf16, 64><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, 1,
                                                        (const bf16*)u, s0, s0 ? kF32 : kNone, (bf16*)y, sT, flag);

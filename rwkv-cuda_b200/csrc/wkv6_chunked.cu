@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(NT, 4)
 wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ k_,
                      const bf16* __restrict__ v_, const void* __restrict__ w_, const bf16* __restrict__ u_,
                      const void* __restrict__ s0_, int s0_kind, bf16* __restrict__ y_, float* __restrict__ sT_,
-                     float* __restrict__ ck_, int* __restrict__ unsafe_) {
+                     float* __restrict__ ck_, int* __restrict__ unsafe_, int flag_div) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* sm = reinterpret_cast<float*>(smem_raw);
     bf16* raw = reinterpret_cast<bf16*>(smem_raw);
@@ -148,7 +148,8 @@ wkv6c_forward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __re
             const float total = Hs[pj] + Hs[N + pj];
             if (phf == 0) {
                 We[pj] = fex2(total);
-                if (-total > kMaxChunkLog2Decay) atomicOr(unsafe_, 1);
+                if (-total > kMaxChunkLog2Decay)   // this (batch, head) unit must be redone by the general-shape kernel
+                    atomicOr(unsafe_ + (((bb / flag_div) * H + hh) & (kChunkedFlagUnits - 1)), 1);
             }
             const int jp = (pj & ~7) + perm8(pj & 7);
             float pprev = phf ? fex2(base) : 1.f;
@@ -614,14 +615,15 @@ wkv6c_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
 }  // namespace v6c
 
-// Flags of the chunked kernels ("a chunk's decay was too strong").  A call enqueues: clear the flag, the
-// chunked kernels (which may raise it), the general-shape kernel (which reads it).  On one stream that is
-// ordered, so every (device, stream) pair owns one slot for good and calls on different streams never share
-// one.  The table holds 256 pairs per process; beyond that the function returns NULL and the caller runs
+// Flags of the chunked kernels ("a chunk's decay was too strong"), one per (batch, head) unit (unit index
+// modulo kChunkedFlagUnits: units that share a flag are redone together).  A call enqueues: clear the flags, the
+// chunked kernels (which may raise some), the general-shape kernel (whose thread blocks read theirs and redo only
+// the flagged units).  On one stream that is ordered, so every (device, stream) pair owns one slot for good and
+// calls on different streams never share one.  The table holds 256 pairs per process; beyond that the function returns NULL and the caller runs
 // the general-shape kernel alone.  (A CUDA graph captured from such a call carries the slot of the
 // capturing stream: replay it on one stream at a time.)
 constexpr int kFlagSlots = 256;
-static __device__ int g_chunked_unsafe[kFlagSlots];
+static __device__ int g_chunked_unsafe[kFlagSlots * kChunkedFlagUnits];
 int* wkv6_chunked_flag(cudaStream_t st) {
     constexpr int kMaxDevices = 64;
     static std::mutex mu;
@@ -637,16 +639,16 @@ int* wkv6_chunked_flag(cudaStream_t st) {
         base[dev] = static_cast<int*>(p);
     }
     for (int i = 0; i < used; ++i)
-        if (owner[i].dev == dev && owner[i].st == st) return base[dev] + i;
+        if (owner[i].dev == dev && owner[i].st == st) return base[dev] + i * kChunkedFlagUnits;
     if (used == kFlagSlots) return nullptr;
     owner[used].dev = dev;
     owner[used].st = st;
-    return base[dev] + used++;
+    return base[dev] + (used++) * kChunkedFlagUnits;
 }
 
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                          const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
-                         cudaStream_t st) {
+                         cudaStream_t st, int flag_div) {
     using namespace v6c;
     RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_forward(chunked): decay mode %d", w_mode);
     dim3 grid(H, B);
@@ -657,7 +659,7 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
         RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         wkv6c_forward_kernel<M, SO><<<grid, NT, FSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, \
                                                                      w, (const bf16*)u, s0, s0_kind, (bf16*)y, sT, ck,  \
-                                                                     unsafe);                                          \
+                                                                     unsafe, flag_div);                                \
     } while (0)
 #define RWKV_GO(M)                    \
     do {                              \

@@ -11,7 +11,7 @@ namespace rwkvb200 {
 // decay is too strong for the chunked form (the results are then invalid).
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                          const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
-                         cudaStream_t st);
+                         cudaStream_t st, int flag_div = 1);   // flag_div: batch rows of this launch per caller's batch row (time-split views)
 
 // Backward; ck are the chunk-start states written by wkv6_chunked_forward on the same inputs
 // (fp32, (B,H,T/16,N,N)).  ds0_kind as s0_kind (0: no state gradient out).  gu is per batch: (B,C).
@@ -22,6 +22,8 @@ int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, con
 // With a static decay (w_mode 2, 3) gw is summed over time into (B,C) instead of written per token.
 
 // one slot of a ring of device flags for `unsafe` (clear it in the stream before the forward)
+// the "decay too strong" flags of the calling stream: kChunkedFlagUnits ints, one per (batch, head) unit modulo that
+constexpr int kChunkedFlagUnits = 1024;
 int* wkv6_chunked_flag(cudaStream_t st);
 
 }  // namespace rwkvb200

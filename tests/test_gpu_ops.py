@@ -369,6 +369,26 @@ def test_wkv6_strong_decay_falls_back(R, shift):
         Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv6 strong decay {name}")
 
 
+def test_wkv6_strong_decay_in_one_unit_only(R):
+    """One (batch, head) unit of six has a decay too strong for the chunked form: only that unit is redone by
+    the general-shape kernels (one flag per unit), every unit's results must be right."""
+    B, T, H, N = 3, 128, 2, 64
+    dtype = torch.bfloat16
+    g = Hh.gen(19)
+    C = H * N
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.randn(g, B, T, C) - 3.0, Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    w_raw[1, 32:64, N:2 * N] += 5.5          # unit (b=1, h=1), tokens 32-63
+    xs = [x.to(dtype).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv6(*xs, H)
+    yo.backward(gy.to(dtype).double())
+    out = run_wkv6(R, dtype, H, r, k, v, w_raw, u, gy)
+    wants = [yo.detach()] + [x.grad for x in xs]
+    for got, want, name in zip(out, wants, ("y", "gr", "gk", "gv", "gw", "gu")):
+        assert torch.isfinite(got.float()).all(), name
+        Hh.assert_close(got, want, Hh.tol_for(dtype), f"wkv6, one unit with a strong decay: {name}")
+
+
 # ------------------------------------------------------------------ RWKV-7
 def run_wkv7(R, dtype, H, inp, use_s0, use_sT, chunk=16):
     B, T, C = inp["r"].shape
