@@ -69,7 +69,8 @@ int rwkvb200_wkv4_backward(int B, int T, int C, const float* w, const float* u, 
  *   w (C,T); k, x, gwk, gk (B,C,T); gw (B,C,T) per-batch partials (caller sums over B).
  *   x[b,c,t] = eps + sum_{u<=t} w[c,(T-1)-(t-u)] k[b,c,u].
  *   Any B and T (the reference requires T%4==0, T<=Tmax, B%BF==0).
- * rwkvb200_timex_backward_reduced writes gw already summed over the batch, shape (C,T).
+ * rwkvb200_timex_backward_reduced writes gw already summed over the batch, shape (C,T); the sum is taken in a
+ * fixed order (the per-row gradients pass through the gk buffer before gk is written).
  */
 int rwkvb200_timex_forward(const float* w, const float* k, float* x, float eps, int B, int C,
                            int T, void* stream);

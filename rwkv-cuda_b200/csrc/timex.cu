@@ -25,7 +25,7 @@
 namespace rwkvb200 {
 namespace {
 
-enum { kFwd = 0, kGk = 1, kGw = 2, kGwSum = 3 };
+enum { kFwd = 0, kGk = 1, kGw = 2 };
 
 template <int MODE, int BG>
 __global__ void __launch_bounds__(1024) timex_kernel(const float* __restrict__ F_, const float* __restrict__ G_,
@@ -105,16 +105,7 @@ __global__ void __launch_bounds__(1024) timex_kernel(const float* __restrict__ F
                 }
             }
 
-            if (MODE == kGwSum) {
-                float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int j = 0; j < BG; ++j)
-#pragma unroll
-                    for (int d = 0; d < 4; ++d) s[d] += acc[j][d];
-#pragma unroll
-                for (int d = 0; d < 4; ++d)
-                    if (t0 + d < T) atomicAdd(out + (i64)c * T + t0 + d, s[d]);
-            } else {
+            {
 #pragma unroll
                 for (int j = 0; j < BG; ++j) {
                     const int b = b0 + j;
@@ -204,8 +195,10 @@ extern "C" int rwkvb200_timex_backward_reduced(const float* w, const float* k, c
                                                float* gk, int B, int C, int T, void* stream) {
     if (int e = check_dims(B, C, T, "timex_backward_reduced")) return e;
     RWKV_NOTNULL(w); RWKV_NOTNULL(k); RWKV_NOTNULL(gwk); RWKV_NOTNULL(gw_sum); RWKV_NOTNULL(gk);
-    cudaError_t ce = cudaMemsetAsync(gw_sum, 0, (size_t)C * T * sizeof(float), as_stream(stream));
-    RWKV_REQUIRE(ce == cudaSuccess, RWKVB200_ECUDA, "timex_backward_reduced: cudaMemsetAsync: %s", cudaGetErrorString(ce));
-    if (int e = launch_any<kGwSum>(gwk, k, gw_sum, 0.f, B, C, T, as_stream(stream), "timex_backward_reduced(gw)")) return e;
+    // The per-row filter gradients go into the gk buffer (same shape, written afterwards), are summed over the
+    // batch in a fixed order, and only then gk is computed: no extra memory, and the sum does not depend on the
+    // order in which thread blocks run (an atomic sum over the batch groups was 3 % faster and did).
+    if (int e = launch_any<kGw>(gwk, k, gk, 0.f, B, C, T, as_stream(stream), "timex_backward_reduced(gw)")) return e;
+    if (int e = rwkvb200_reduce_batch_partials(RWKVB200_F32, B, C * T, gk, gw_sum, stream)) return e;
     return launch_any<kGk>(w, gwk, gk, 0.f, B, C, T, as_stream(stream), "timex_backward_reduced(gk)");
 }
