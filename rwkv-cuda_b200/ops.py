@@ -63,6 +63,14 @@ def scratch(nbytes, device):
     return buf
 
 
+def free_scratch(device=None):
+    """Drops the cached scratch buffers (of one device, or of all): they grow to the largest request seen per
+    (device, stream) and are otherwise kept for the life of the process.  Call it with no work of this library
+    in flight on those streams."""
+    for key in [k for k in _scratch if device is None or k[0] == torch.device(device).index]:
+        del _scratch[key]
+
+
 # ---- RWKV-4 (wkv/cuda/wkv_op.cpp:6-11) ------------------------------------------------
 def wkv4_forward(B, T, C, w, u, k, v, y):
     f = torch.float32
