@@ -2,6 +2,7 @@
 // between the general-shape kernels and the N = 64 tensor-core path).
 #include "common.cuh"
 #include "wkv7_dispatch.cuh"
+#include "wkv6_chunked.cuh"
 #include <atomic>
 #include <initializer_list>
 
@@ -114,19 +115,20 @@ extern "C" int rwkvb200_device_status(void) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
-    const int p = wkv7_l32_bwdp_error(0), q = wkv7_l32_fwdp_error(0);
-    if (p < 0 || q < 0) {
+    const int p = wkv7_l32_bwdp_error(0), q = wkv7_l32_fwdp_error(0), r6 = wkv6_l32_error(0);
+    if (p < 0 || q < 0 || r6 < 0) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
     if (f) return 10 + f;
     if (g) return 20 + g;
     if (p) return p;            // the two-stage backward records 30.. (front group) or 40.. (back group)
-    return q ? q + 20 : 0;      // the two-stage forward 50.. / 60..
+    if (q) return q + 20;       // the staged RWKV-7 forward 50.. / 55.. / 60..
+    return r6 ? r6 + 40 : 0;    // the staged RWKV-6 / RWKV-5 forward 70.. / 75.. / 80..
 }
 
 extern "C" int rwkvb200_device_status_clear(void) {
-    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0 && wkv7_l32_fwdp_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
+    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0 && wkv7_l32_fwdp_error(1) == 0 && wkv6_l32_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
     return RWKVB200_OK;
 }
 

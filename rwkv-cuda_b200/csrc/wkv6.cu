@@ -447,6 +447,14 @@ extern "C" int rwkvb200_wkv6state_forward_ex(int dtype, int B, int T, int C, int
                : launch_fwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, sk, y, sT, as_stream(stream), "wkv6state_forward_ex");
 }
 
+// Kernel of the bf16 / head-size-64 forward of RWKV-5 and RWKV-6: 1 (default) = tcgen05, 32-token chunks, three warp
+// groups, inputs by TMA (wkv6_l32_fwd.cu); 0 = mma.sync, 16-token chunks (wkv6_chunked.cu).  For tests and measurements.
+extern "C" int rwkvb200_wkv6_select_forward(int kernel) {
+    RWKV_REQUIRE(kernel == 0 || kernel == 1, RWKVB200_EINVAL, "wkv6_select_forward: kernel %d not in 0..1", kernel);
+    wkv6_select_forward(kernel);
+    return RWKVB200_OK;
+}
+
 // The forward split over time (wkv6_tsplit.cu): `segments` pieces of T/segments tokens run at the same time.
 // Tensor-core shapes only (bf16, head size 64, T/segments a multiple of 16, 16-byte aligned tensors); a decay too
 // strong for the chunked form makes the general-shape kernel redo the whole call, as in the unsplit forward.

@@ -646,10 +646,19 @@ int* wkv6_chunked_flag(cudaStream_t st) {
     return base[dev] + (used++) * kChunkedFlagUnits;
 }
 
+static std::atomic<int> g_wkv6_forward_tcgen05{1};
+void wkv6_select_forward(int tcgen05) { g_wkv6_forward_tcgen05.store(tcgen05 ? 1 : 0); }
+int wkv6_forward_choice() { return g_wkv6_forward_tcgen05.load(); }
+
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
                          const void* u, const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe,
                          cudaStream_t st, int flag_div) {
     using namespace v6c;
+    // a forward that leaves no chunk states for a backward pass: the tcgen05 kernel where it can run
+    if (y != nullptr && ck == nullptr && unsafe != nullptr && g_wkv6_forward_tcgen05.load()) {
+        const int rc = wkv6_l32_forward(B, T, H, r, k, v, w, w_mode, u, s0, s0_kind, y, sT, unsafe, st, flag_div);
+        if (rc != 1) return rc;
+    }
     RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_forward(chunked): decay mode %d", w_mode);
     dim3 grid(H, B);
 #define RWKV_GO1(M, SO)                                                                                                \

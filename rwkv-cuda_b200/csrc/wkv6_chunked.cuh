@@ -22,6 +22,15 @@ int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, con
 // With a static decay (w_mode 2, 3) gw is summed over time into (B,C) instead of written per token.
 
 // one slot of a ring of device flags for `unsafe` (clear it in the stream before the forward)
+// The same forward (without saved chunk states) on tcgen05: 32-token chunks, three warp groups, inputs by TMA
+// (wkv6_l32_fwd.cu).  Returns 1 when tensor maps cannot be made here: the caller then uses wkv6_chunked_forward.
+int wkv6_l32_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode, const void* u,
+                     const void* s0, int s0_kind, void* y, float* sT, int* unsafe, cudaStream_t st, int flag_div = 1);
+int wkv6_l32_error(int clear);   // sticky status word of that kernel: read (clear = 0) or reset (clear = 1)
+// 0 = the mma.sync kernel of wkv6_chunked.cu for every forward, 1 (default) = the tcgen05 kernel where it applies
+void wkv6_select_forward(int tcgen05);
+int wkv6_forward_choice();
+
 // the "decay too strong" flags of the calling stream: kChunkedFlagUnits ints, one per (batch, head) unit modulo that
 constexpr int kChunkedFlagUnits = 1024;
 int* wkv6_chunked_flag(cudaStream_t st);

@@ -143,3 +143,62 @@ def test_split_pays_for_a_single_sequence(R):
     t_split = timed(lambda: R.ops.wkv6state_forward_tsplit(B, T, C, H, r, k, v, w, u, s0, y, sT))
     print(f"RWKV-6 forward B1 T4096 H64: unsplit {t_plain:.3f} ms, split into {K} segments (automatic) {t_split:.3f} ms")
     assert t_split < 0.8 * t_plain
+
+
+@pytest.mark.parametrize("B,T,H", [(2, 256, 3), (1, 48, 2), (1, 2048, 1)])
+def test_rwkv6_forward_kernels_agree(R, B, T, H):
+    """The tcgen05 forward (32-token chunks) and the mma.sync forward (16-token chunks) of RWKV-6 with state:
+    both against the oracle, and close to each other; the times of the benchmark shape are printed."""
+    from rwkv_cuda_b200 import _lib
+    N = 64
+    C = H * N
+    r, k, v, w_raw, u, s0 = _v6_inputs(B, T, H, N, seed=31)
+    xs = [x.to(BF).double() for x in (r, k, v, w_raw, u)]
+    yo, sTo = O.wkv6(*xs, H, s0=s0.double(), return_state=True)
+    rd, kd, vd, wd, ud = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, w_raw, u))
+    outs = {}
+    try:
+        for kern in (0, 1):
+            _lib.call("rwkvb200_wkv6_select_forward", kern)
+            y, sT = torch.full((B, T, C), float("nan"), dtype=BF, device=DEV), torch.full((B, H, N, N), float("nan"), device=DEV)
+            R.ops.wkv6state_forward_ex(B, T, C, H, rd, kd, vd, wd, ud, s0.to(DEV), y, sT)
+            torch.cuda.synchronize()
+            assert _lib.lib().rwkvb200_device_status() == 0
+            Hh.assert_close(y, yo, Hh.TOL_BF16, f"y, forward kernel {kern}")
+            Hh.assert_close(sT, sTo, Hh.TOL_BF16, f"sT, forward kernel {kern}")
+            outs[kern] = (y, sT)
+    finally:
+        _lib.call("rwkvb200_wkv6_select_forward", 1)
+    Hh.assert_close(outs[1][0], outs[0][0].double().cpu(), Hh.TOL_BF16, "y, tcgen05 against mma.sync")
+
+
+def test_rwkv6_forward_kernel_times(R):
+    from rwkv_cuda_b200 import _lib
+    B, T, H, N = 16, 4096, 64, 64
+    C = H * N
+    g = torch.Generator(device=DEV)
+    g.manual_seed(5)
+    mk = lambda sc=0.5: (sc * torch.randn(B, T, C, generator=g, device=DEV)).to(BF)
+    r, k, v = mk(), mk(), mk()
+    w = (torch.randn(B, T, C, generator=g, device=DEV) - 3.0).to(BF)
+    u = (torch.rand(H, N, generator=g, device=DEV) * 2 - 1).to(BF)
+    s0 = 0.1 * torch.randn(B, H, N, N, generator=g, device=DEV)
+    y, sT = torch.empty(B, T, C, dtype=BF, device=DEV), torch.empty_like(s0)
+    times = {}
+    try:
+        for kern in (0, 1):
+            _lib.call("rwkvb200_wkv6_select_forward", kern)
+            for _ in range(3):
+                R.ops.wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                R.ops.wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT)
+            e1.record()
+            torch.cuda.synchronize()
+            times[kern] = e0.elapsed_time(e1) / 10
+    finally:
+        _lib.call("rwkvb200_wkv6_select_forward", 1)
+    print(f"RWKV-6 forward B16 T4096 H64: mma.sync {times[0]:.3f} ms, tcgen05 {times[1]:.3f} ms")
+    assert _lib.lib().rwkvb200_device_status() == 0
