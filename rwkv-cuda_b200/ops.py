@@ -259,12 +259,16 @@ def wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT):
 
 
 def tsplit_segments(B, T, H, device):
-    """How many time segments the split forward should use for this launch: enough to fill the four thread
-    blocks that an SM holds, at least 256 tokens per segment, whole 16-token chunks; 1 when the launch fills
-    the GPU by itself (measured for one sequence of 64 heads, T 4096: 0.46 ms unsplit, 0.44 / 0.30 / 0.27 /
-    0.32 ms with 2 / 4 / 8 / 16 segments)."""
+    """How many time segments the split forward should use for this launch: 1 unless the launch has at most a
+    quarter as many (batch, head) units as the GPU has SMs (the unsplit tcgen05 forward walks a unit's chunks at
+    about 2.5 k cycles per 32 tokens, which a split only beats with many idle SMs); then one segment per idle SM,
+    at least 512 tokens each, whole 16-token chunks.  Measured, RWKV-6 with state, one sequence of 8 heads:
+    T 16384 0.61 ms unsplit, 0.29 ms in 16 segments; T 65536 2.43 -> 0.73 ms; 64 heads: the split loses."""
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    k = max(1, min(4 * sms // max(1, B * H), T // 256))
+    units = max(1, B * H)
+    if units * 4 > sms:
+        return 1
+    k = max(1, min(sms // units, T // 512))
     while k > 1 and (T % k != 0 or (T // k) % 16 != 0):
         k -= 1
     return k
