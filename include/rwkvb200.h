@@ -193,8 +193,8 @@ int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const 
                                    void* gk, void* gv, void* gw, void* gu, float* ds0,
                                    void* scratch, void* stream);
 
-/* Kernel of the bf16 / head-size-64 forward of RWKV-5 and RWKV-6: 1 (default) = tcgen05 (32-token chunks, three
- * warp groups on consecutive chunks, inputs by TMA), 0 = mma.sync (16-token chunks).  Results agree to rounding.
+/* Kernels of the bf16 / head-size-64 forward and backward of RWKV-5 and RWKV-6: 1 (default) = tcgen05 (32-token
+ * chunks; the forward as three warp groups with inputs by TMA), 0 = mma.sync (16-token chunks).  Results agree to rounding.
  * Process-wide, for tests and measurements; no counterpart in the reference. */
 int rwkvb200_wkv6_select_forward(int kernel);
 
@@ -264,7 +264,7 @@ int rwkvb200_wkv7_select_form(int form);
 /* Synchronous read of the current device's sticky status word: 0, or 10 + n / 20 + n when the n-th
  * bounded wait of the tensor-core forward / backward ran out in some thread block (30.. / 40..: the
  * front / back warp group of the two-stage backward, 50.. / 55.. / 60..: loader / matrix / chain group of the
- * staged forward; 70.. / 75.. / 80..: the same groups of the staged RWKV-6 / RWKV-5 forward) (the outputs of
+ * staged forward; 70.. / 75.. / 80..: the same groups of the staged RWKV-6 / RWKV-5 forward; 91..: their tcgen05 backward) (the outputs of
  * that call are then invalid); negative on a CUDA error.  Per device; stays set until cleared. */
 int rwkvb200_device_status(void);
 /* Resets the current device's status word.  No counterpart in the reference. */

@@ -115,8 +115,8 @@ extern "C" int rwkvb200_device_status(void) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
-    const int p = wkv7_l32_bwdp_error(0), q = wkv7_l32_fwdp_error(0), r6 = wkv6_l32_error(0);
-    if (p < 0 || q < 0 || r6 < 0) {
+    const int p = wkv7_l32_bwdp_error(0), q = wkv7_l32_fwdp_error(0), r6 = wkv6_l32_error(0), b6 = wkv6_l32_bwd_error(0);
+    if (p < 0 || q < 0 || r6 < 0 || b6 < 0) {
         set_error("device_status: reading the status words failed");
         return RWKVB200_ECUDA;
     }
@@ -124,11 +124,12 @@ extern "C" int rwkvb200_device_status(void) {
     if (g) return 20 + g;
     if (p) return p;            // the two-stage backward records 30.. (front group) or 40.. (back group)
     if (q) return q + 20;       // the staged RWKV-7 forward 50.. / 55.. / 60..
-    return r6 ? r6 + 40 : 0;    // the staged RWKV-6 / RWKV-5 forward 70.. / 75.. / 80..
+    if (r6) return r6 + 40;     // the staged RWKV-6 / RWKV-5 forward 70.. / 75.. / 80..
+    return b6 ? b6 + 90 : 0;    // the tcgen05 RWKV-6 / RWKV-5 backward 91..
 }
 
 extern "C" int rwkvb200_device_status_clear(void) {
-    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0 && wkv7_l32_fwdp_error(1) == 0 && wkv6_l32_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
+    RWKV_REQUIRE(wkv7_l32_clear_errors() == 0 && wkv7_l32_bwdp_error(1) == 0 && wkv7_l32_fwdp_error(1) == 0 && wkv6_l32_error(1) == 0 && wkv6_l32_bwd_error(1) == 0, RWKVB200_ECUDA, "device_status_clear: writing the status words failed");
     return RWKVB200_OK;
 }
 

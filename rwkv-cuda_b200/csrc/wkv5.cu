@@ -282,8 +282,8 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         if (flag != nullptr) {
             RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA, "wkv5_backward: clearing the device flag failed");
             float* ck = static_cast<float*>(scratch);
-            if (int e = wkv6_chunked_forward(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, nullptr, nullptr, ck, flag, st)) return e;
-            if (int e = wkv6_chunked_backward(B, T, H, r, k, v, ww1, 3, u1, gy, nullptr, ck, gr, gk, gv, gw1, gu1, nullptr, 0, st, gw32, gu32))
+            if (int e = wkv6_backward_with_states(B, T, H, r, k, v, ww1, 3, u1, nullptr, 0, gy, nullptr, ck, gr, gk, gv, gw1, gu1,
+                                                  nullptr, 0, flag, st, gw32, gu32))
                 return e;
             only_if = flag;
         }

@@ -295,8 +295,8 @@ int launch_bwd(int B, int T, int C, int H, const void* r, const void* k, const v
         if (flag != nullptr) {
             RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA, "%s: clearing the device flag failed", what);
             float* ck = static_cast<float*>(scratch);
-            if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, nullptr, nullptr, ck, flag, st)) return e;
-            if (int e = wkv6_chunked_backward(B, T, H, r, k, v, w, w_raw, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st))
+            if (int e = wkv6_backward_with_states(B, T, H, r, k, v, w, w_raw, u, s0, s0_kind, gy, dsT, ck, gr, gk, gv, gw, gu, ds0,
+                                                  ds0_kind, flag, st))
                 return e;
             only_if = flag;
         }
@@ -447,11 +447,12 @@ extern "C" int rwkvb200_wkv6state_forward_ex(int dtype, int B, int T, int C, int
                : launch_fwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, sk, y, sT, as_stream(stream), "wkv6state_forward_ex");
 }
 
-// Kernel of the bf16 / head-size-64 forward of RWKV-5 and RWKV-6: 1 (default) = tcgen05, 32-token chunks, three warp
-// groups, inputs by TMA (wkv6_l32_fwd.cu); 0 = mma.sync, 16-token chunks (wkv6_chunked.cu).  For tests and measurements.
+// Kernels of the bf16 / head-size-64 forward and backward of RWKV-5 and RWKV-6: 1 (default) = tcgen05, 32-token chunks
+// (wkv6_l32_fwd.cu, wkv6_l32_bwd.cu); 0 = mma.sync, 16-token chunks (wkv6_chunked.cu).  For tests and measurements.
 extern "C" int rwkvb200_wkv6_select_forward(int kernel) {
     RWKV_REQUIRE(kernel == 0 || kernel == 1, RWKVB200_EINVAL, "wkv6_select_forward: kernel %d not in 0..1", kernel);
     wkv6_select_forward(kernel);
+    wkv6_select_backward(kernel);
     return RWKVB200_OK;
 }
 

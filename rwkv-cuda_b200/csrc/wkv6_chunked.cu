@@ -646,8 +646,9 @@ int* wkv6_chunked_flag(cudaStream_t st) {
     return base[dev] + (used++) * kChunkedFlagUnits;
 }
 
-static std::atomic<int> g_wkv6_forward_tcgen05{1};
+static std::atomic<int> g_wkv6_forward_tcgen05{1}, g_wkv6_backward_tcgen05{1};
 void wkv6_select_forward(int tcgen05) { g_wkv6_forward_tcgen05.store(tcgen05 ? 1 : 0); }
+void wkv6_select_backward(int tcgen05) { g_wkv6_backward_tcgen05.store(tcgen05 ? 1 : 0); }
 int wkv6_forward_choice() { return g_wkv6_forward_tcgen05.load(); }
 
 int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
@@ -656,7 +657,7 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
     using namespace v6c;
     // a forward that leaves no chunk states for a backward pass: the tcgen05 kernel where it can run
     if (y != nullptr && ck == nullptr && unsafe != nullptr && g_wkv6_forward_tcgen05.load()) {
-        const int rc = wkv6_l32_forward(B, T, H, r, k, v, w, w_mode, u, s0, s0_kind, y, sT, unsafe, st, flag_div);
+        const int rc = wkv6_l32_forward(B, T, H, r, k, v, w, w_mode, u, s0, s0_kind, y, sT, nullptr, unsafe, st, flag_div);
         if (rc != 1) return rc;
     }
     RWKV_REQUIRE(w_mode >= 0 && w_mode <= 3, RWKVB200_EINVAL, "wkv6_forward(chunked): decay mode %d", w_mode);
@@ -684,6 +685,23 @@ int wkv6_chunked_forward(int B, int T, int H, const void* r, const void* k, cons
 #undef RWKV_GO
 #undef RWKV_GO1
     return check_launch("wkv6_forward(chunked)");
+}
+
+// The backward with its pass that rebuilds the chunk-start states into `ck` (the caller's scratch buffer): on the
+// tcgen05 kernels (32-token chunks) where they can run, else on the mma.sync kernels (16-token chunks).
+int wkv6_backward_with_states(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
+                              const void* u, const void* s0, int s0_kind, const void* gy, const float* dsT, float* ck, void* gr,
+                              void* gk, void* gv, void* gw, void* gu, void* ds0, int ds0_kind, int* unsafe, cudaStream_t st,
+                              float* gw32, float* gu32) {
+    if (unsafe != nullptr && g_wkv6_backward_tcgen05.load()) {
+        const int rc = wkv6_l32_forward(B, T, H, r, k, v, w, w_mode, u, s0, s0_kind, nullptr, nullptr, ck, unsafe, st, 1);
+        if (rc != 1) {
+            if (rc != 0) return rc;
+            return wkv6_l32_backward(B, T, H, r, k, v, w, w_mode, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st, gw32, gu32);
+        }
+    }
+    if (int e = wkv6_chunked_forward(B, T, H, r, k, v, w, w_mode, u, s0, s0_kind, nullptr, nullptr, ck, unsafe, st)) return e;
+    return wkv6_chunked_backward(B, T, H, r, k, v, w, w_mode, u, gy, dsT, ck, gr, gk, gv, gw, gu, ds0, ds0_kind, st, gw32, gu32);
 }
 
 int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,

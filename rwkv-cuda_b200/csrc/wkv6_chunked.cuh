@@ -25,10 +25,20 @@ int wkv6_chunked_backward(int B, int T, int H, const void* r, const void* k, con
 // The same forward (without saved chunk states) on tcgen05: 32-token chunks, three warp groups, inputs by TMA
 // (wkv6_l32_fwd.cu).  Returns 1 when tensor maps cannot be made here: the caller then uses wkv6_chunked_forward.
 int wkv6_l32_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode, const void* u,
-                     const void* s0, int s0_kind, void* y, float* sT, int* unsafe, cudaStream_t st, int flag_div = 1);
+                     const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe, cudaStream_t st, int flag_div = 1);
+// The backward on tcgen05 (wkv6_l32_bwd.cu); ck: chunk-start states every 32 tokens from wkv6_l32_forward.
+int wkv6_l32_backward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode, const void* u,
+                      const void* gy, const float* dsT, const float* ck, void* gr, void* gk, void* gv, void* gw, void* gu,
+                      void* ds0, int ds0_kind, cudaStream_t st, float* gw32 = nullptr, float* gu32 = nullptr);
+int wkv6_l32_bwd_error(int clear);
 int wkv6_l32_error(int clear);   // sticky status word of that kernel: read (clear = 0) or reset (clear = 1)
 // 0 = the mma.sync kernel of wkv6_chunked.cu for every forward, 1 (default) = the tcgen05 kernel where it applies
 void wkv6_select_forward(int tcgen05);
+void wkv6_select_backward(int tcgen05);
+int wkv6_backward_with_states(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode,
+                              const void* u, const void* s0, int s0_kind, const void* gy, const float* dsT, float* ck, void* gr,
+                              void* gk, void* gv, void* gw, void* gu, void* ds0, int ds0_kind, int* unsafe, cudaStream_t st,
+                              float* gw32 = nullptr, float* gu32 = nullptr);
 int wkv6_forward_choice();
 
 // the "decay too strong" flags of the calling stream: kChunkedFlagUnits ints, one per (batch, head) unit modulo that

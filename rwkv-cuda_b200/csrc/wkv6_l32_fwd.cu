@@ -79,7 +79,7 @@ template <int WMODE>
 __global__ void __launch_bounds__(PNT, 1)
 wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void* __restrict__ wstat_, const bf16* __restrict__ u_,
                      const void* __restrict__ s0_, int s0_kind, bf16* __restrict__ y_, float* __restrict__ sT_,
-                     int* __restrict__ unsafe_, int flag_div) {
+                     float* __restrict__ ck_, int* __restrict__ unsafe_, int flag_div) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     bf16* ystage = reinterpret_cast<bf16*>(smem + Smem::kY);
@@ -98,6 +98,8 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
     const i64 sbase = (i64)(bb * H + hh) * 64 * 64;
     const int nchunks = (T + LC - 1) / LC;
     constexpr bool kPerToken = WMODE < 2;
+    float* ck = ck_ ? ck_ + (i64)(bb * H + hh) * nchunks * 64 * 64 : nullptr;   // chunk-start states for a backward pass
+    const bool states_only = y_ == nullptr;                                  // no y: the pass that only saves the states
     constexpr int kWTile = WMODE == 0 ? 8192 : 4096;
 
     if (tid == 0) {
@@ -241,6 +243,11 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
             group_sync(gbar, GNT);
             tc_fence_after();
             if (gabort[1]) break;
+            if (states_only) {   // nothing to build: hand the sets on
+                if (gtid == 0) { mbar_arrive(bar + kEmptyA + sa); mbar_arrive(bar + kFullU + su); }
+                if (++sa == NA) { sa = 0; ++ua; }
+                continue;
+            }
             if (wg == 0) {   // [K~;K^] R~^T: rows 0-31 = k~_s, 32-63 = k^_s; columns = tokens t
                 const uint32_t kkA = smem_u32(A + ARR32), rtA = smem_u32(A);
 #pragma unroll
@@ -291,6 +298,13 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
                     Sd[nt][e] = s0_kind == 2 ? reinterpret_cast<const float*>(s0_)[idx]
                               : s0_kind == 1 ? __bfloat162float(reinterpret_cast<const bf16*>(s0_)[idx]) : 0.f;
                 }
+            if (ck != nullptr) {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    *reinterpret_cast<float2*>(ck + (row0 + g) * 64 + nt * 8 + 2 * t) = make_float2(Sd[nt][0], Sd[nt][1]);
+                    *reinterpret_cast<float2*>(ck + (row0 + g + 8) * 64 + nt * 8 + 2 * t) = make_float2(Sd[nt][2], Sd[nt][3]);
+                }
+            }
             tmem_st_tiles<8>(tmS + lane_off, Sd);
             tmem_wait_st();
         }
@@ -311,23 +325,25 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
             tc_fence_after();
             if (gabort[2]) break;
             if (wg == 0) {
+                if (!states_only) {
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)   // X = S R~^T
-                    mma_ts(tmX, tmS + ks * 8, desc_k(rtA, 0, ks * 8, HALF32), idesc64(32, 0, 0), ks > 0, lead);
+                    for (int ks = 0; ks < 8; ++ks)   // X = S R~^T
+                        mma_ts(tmX, tmS + ks * 8, desc_k(rtA, 0, ks * 8, HALF32), idesc64(32, 0, 0), ks > 0, lead);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // Y = X + V A
-                    mma_ss(tmX, desc_mn(vA, ks * 8, HALF32), desc_mn(amA, ks * 8, HALF32), idesc64(32, 1, 1), 1, lead);
-                mma_commit(bar + kBY, lead);
-                cs.sync(lead);                   // X has read S: it may be updated
+                    for (int ks = 0; ks < 4; ++ks)   // Y = X + V A
+                        mma_ss(tmX, desc_mn(vA, ks * 8, HALF32), desc_mn(amA, ks * 8, HALF32), idesc64(32, 1, 1), 1, lead);
+                    mma_commit(bar + kBY, lead);
+                    cs.sync(lead);                   // X has read S: it may be updated
+                }
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)   // S += V K~
                     mma_ss(tmS, desc_mn(vA, ks * 8, HALF32), desc_mn(kkA, ks * 8, HALF64), idesc64(64, 1, 1), 1, lead);
                 mma_commit(bar + kBS, lead);
                 if (cs.fail) fail = 41;
             }
-            if (!mbar_wait(bar + kBY, par)) fail = 42;
+            if (!states_only && !mbar_wait(bar + kBY, par)) fail = 42;
             tc_fence_after();
-            {
+            if (!states_only) {
                 float Y[4][4];
                 tmem_ld_tiles<4>(Y, tmX + lane_off);
                 tmem_wait_ld();
@@ -341,7 +357,7 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
             }
             tc_fence_before();
             group_sync(gbar, GNT);
-            {
+            if (!states_only) {
                 const int tt = gtid >> 2, seg = gtid & 3;   // token, 16 channels
                 if (tt < valid) {
                     const uint4* sp = reinterpret_cast<const uint4*>(ystage + tt * 72 + seg * 16);
@@ -353,7 +369,7 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
             if (!mbar_wait(bar + kBS, par)) fail = 43;
             tc_fence_after();
             {
-                float* dst = (c + 1 == nchunks && sT_ != nullptr) ? sT_ + sbase : nullptr;
+                float* dst = (c + 1 < nchunks) ? (ck ? ck + (i64)(c + 1) * 64 * 64 : nullptr) : (sT_ ? sT_ + sbase : nullptr);
                 float Sd[8][4];
                 tmem_ld_tiles<8>(Sd, tmS + lane_off);
                 tmem_wait_ld();
@@ -385,7 +401,7 @@ wkv6q_forward_kernel(int T, int H, const __grid_constant__ Maps maps, const void
     const int ab = *abort_word;
     if (ab && tid == 0) {   // a wait ran out: record it and poison this unit's outputs
         atomicMax(&g_v6q_error, ab);
-        y_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
+        if (y_ != nullptr) y_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
     }
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tm0) : "memory");
 }
@@ -418,9 +434,10 @@ bool make_map6(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, b
 }  // namespace
 
 // Returns RWKVB200_OK, an error code, or 1 when tensor maps cannot be made here (the caller then uses the
-// mma.sync kernel of wkv6_chunked.cu).  Arguments as wkv6_chunked_forward, without the saved chunk states.
+// mma.sync kernel of wkv6_chunked.cu).  Arguments as wkv6_chunked_forward; ck (optional): the states at the start of
+// every 32-token chunk, (B,H,ceil(T/32),N,N) fp32, for wkv6_l32_backward; y may then be NULL (states only).
 int wkv6_l32_forward(int B, int T, int H, const void* r, const void* k, const void* v, const void* w, int w_mode, const void* u,
-                     const void* s0, int s0_kind, void* y, float* sT, int* unsafe, cudaStream_t st, int flag_div) {
+                     const void* s0, int s0_kind, void* y, float* sT, float* ck, int* unsafe, cudaStream_t st, int flag_div) {
     using namespace v6q;
     if (encode_tiled6() == nullptr) return 1;
     Maps maps;
@@ -438,7 +455,7 @@ int wkv6_l32_forward(int B, int T, int H, const void* r, const void* k, const vo
         cudaError_t e = cudaFuncSetAttribute(wkv6q_forward_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes); \
         RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv6_forward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));  \
         wkv6q_forward_kernel<M><<<grid, PNT, Smem::kBytes, st>>>(T, H, maps, w, (const bf16*)u, s0, s0_kind, (bf16*)y, sT, \
-                                                                unsafe, flag_div);                                       \
+                                                                ck, unsafe, flag_div);                                       \
     } while (0)
     switch (w_mode) {
         case 0: RWKV_GO(0); break;

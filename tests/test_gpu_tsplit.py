@@ -202,3 +202,39 @@ def test_rwkv6_forward_kernel_times(R):
         _lib.call("rwkvb200_wkv6_select_forward", 1)
     print(f"RWKV-6 forward B16 T4096 H64: mma.sync {times[0]:.3f} ms, tcgen05 {times[1]:.3f} ms")
     assert _lib.lib().rwkvb200_device_status() == 0
+
+
+@pytest.mark.parametrize("B,T,H", [(2, 256, 3), (1, 48, 2), (1, 1024, 1)])
+def test_rwkv6_backward_kernels_agree(R, B, T, H):
+    """The tcgen05 backward (32-token chunks) and the mma.sync backward (16-token chunks) of RWKV-6 with state and a
+    gradient of the final state: both against autograd through the fp64 oracle, and close to each other."""
+    from rwkv_cuda_b200 import _lib
+    N = 64
+    C = H * N
+    r, k, v, w_raw, u, s0 = _v6_inputs(B, T, H, N, seed=37)
+    g = Hh.gen(38)
+    gy, dsT = Hh.randn(g, B, T, C), Hh.randn(g, B, H, N, N)
+    xs = [x.to(BF).double().requires_grad_(True) for x in (r, k, v, w_raw, u)] + [s0.double().requires_grad_(True)]
+    yo, sTo = O.wkv6(*xs[:5], H, s0=xs[5], return_state=True)
+    torch.autograd.backward([yo, sTo], [gy.to(BF).double(), dsT.double()])
+    rd, kd, vd, wd, ud, gd = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, w_raw, u, gy))
+    s0d, dsTd = s0.to(DEV), dsT.to(DEV)
+    names = ("gr", "gk", "gv", "gw", "gu", "ds0")
+    outs = {}
+    try:
+        for kern in (0, 1):
+            _lib.call("rwkvb200_wkv6_select_forward", kern)
+            nan = float("nan")
+            gr, gk, gv, gw = (torch.full((B, T, C), nan, dtype=BF, device=DEV) for _ in range(4))
+            gu, ds0 = torch.full((B, C), nan, dtype=BF, device=DEV), torch.full((B, H, N, N), nan, device=DEV)
+            R.ops.wkv6state_backward_ex(B, T, C, H, rd, kd, vd, wd, ud, s0d, gd, dsTd, gr, gk, gv, gw, gu, ds0)
+            torch.cuda.synchronize()
+            assert _lib.lib().rwkvb200_device_status() == 0
+            got = (gr, gk, gv, gw, gu.float().sum(0), ds0)
+            for x, want, name in zip(got, [xx.grad for xx in xs], names):
+                Hh.assert_close(x, want, Hh.TOL_BF16, f"{name}, backward kernel {kern}")
+            outs[kern] = got
+    finally:
+        _lib.call("rwkvb200_wkv6_select_forward", 1)
+    for a, b, name in zip(outs[1], outs[0], names):
+        Hh.assert_close(a, b.double().cpu(), Hh.TOL_BF16, f"{name}, tcgen05 against mma.sync")
