@@ -348,8 +348,15 @@ def run_secondary(op, args):
         y, gr, gk, gv, gw = (torch.empty(B, T, C, dtype=bf, device=dev) for _ in range(5))
         gu = torch.empty(B, C, dtype=bf, device=dev)
         sT, ds0 = torch.empty_like(s0), torch.empty_like(s0)
-        fwd = lambda: R.ops.wkv6state_forward_ex(B, T, C, H, r, k, v, wraw, u, s0, y, sT)
-        bwd = lambda: R.ops.wkv6state_backward_ex(B, T, C, H, r, k, v, wraw, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0)
+        # the training flow: the forward keeps the chunk-start states for the backward
+        saved = torch.empty(R.ops.wkv6_saved_bytes(B, T, C), dtype=torch.uint8, device=dev)
+        valid = [False]
+
+        def fwd():
+            valid[0] = R.ops.wkv6state_forward_saved(B, T, C, H, r, k, v, wraw, u, s0, y, sT, saved)
+
+        def bwd():
+            R.ops.wkv6state_backward_saved(B, T, C, H, r, k, v, wraw, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0, saved, valid[0])
         st = 4 * B * H * N * N
         bytes_f, bytes_b = 10 * C * B * T + 2 * st, 18 * C * B * T + 2 * st
         bound, note = "hbm", "chunked tensor-core kernels (mma.sync TF32), per-token decay, fp32 state in/out"

@@ -193,6 +193,21 @@ int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const 
                                    void* gk, void* gv, void* gw, void* gu, float* ds0,
                                    void* scratch, void* stream);
 
+/* RWKV-6 with fp32 state, training flow with saved states: the forward leaves the states at the start of every
+ * 32-token chunk in `saved` (rwkvb200_wkv6_scratch_bytes(B,T,C) bytes of device memory, kept by the caller until the
+ * backward), so that the backward need not run over the sequence once more to rebuild them.  The forward returns
+ * RWKVB200_OK when it saved them, 1 when it ran on kernels that do not (pass saved_valid = 0 then: the backward behaves
+ * as rwkvb200_wkv6state_backward_ex with `saved` as scratch), a negative code on error.  No counterpart in the
+ * reference, whose operator recomputes everything in the backward (wkv6state_cuda_v1a.cu). */
+int rwkvb200_wkv6state_forward_saved(int dtype, int B, int T, int C, int H, const void* r,
+                                     const void* k, const void* v, const void* w, const void* u,
+                                     const float* s0, void* y, float* sT, void* saved, void* stream);
+int rwkvb200_wkv6state_backward_saved(int dtype, int B, int T, int C, int H, const void* r,
+                                      const void* k, const void* v, const void* w, const void* u,
+                                      const float* s0, const void* gy, const float* dsT, void* gr,
+                                      void* gk, void* gv, void* gw, void* gu, float* ds0,
+                                      void* saved, int saved_valid, void* stream);
+
 /* Kernels of the bf16 / head-size-64 forward and backward of RWKV-5 and RWKV-6: 1 (default) = tcgen05 (32-token
  * chunks; the forward as three warp groups with inputs by TMA), 0 = mma.sync (16-token chunks).  Results agree to rounding.
  * Process-wide, for tests and measurements; no counterpart in the reference. */

@@ -492,6 +492,74 @@ extern "C" int rwkvb200_wkv6state_forward_tsplit(int dtype, int B, int T, int C,
     return check_launch("wkv6state_forward_tsplit");
 }
 
+// Training flow with saved states: the forward leaves the states at the start of every 32-token chunk (and the
+// "decay too strong" flags of its units) in `saved`, a buffer of rwkvb200_wkv6_scratch_bytes(B,T,C) bytes, and the
+// backward uses them instead of running its own pass over the sequence to rebuild them.  The forward returns
+// RWKVB200_OK when it saved them and 1 when it ran on kernels that do not (other dtype, head size, alignment, no
+// tensor maps, no flag words left): pass that as `saved_valid` = 0 to the backward, which then behaves as
+// rwkvb200_wkv6state_backward_ex with `saved` as its scratch.  No counterpart in the reference.
+extern "C" int rwkvb200_wkv6state_forward_saved(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                                const void* v, const void* w, const void* u, const float* s0, void* y,
+                                                float* sT, void* saved, void* stream) {
+    if (int e = check_dims("wkv6state_forward_saved", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(y); RWKV_NOTNULL(saved);
+    const int N = C / H, sk = s0 ? kF32 : kNone;
+    cudaStream_t st = as_stream(stream);
+    int* flag = nullptr;
+    if (dtype == RWKVB200_BF16 && wkv6_forward_choice() && chunked_ok<bf16>(T, N, {r, k, v, w, u, s0, y, sT, saved}))
+        flag = wkv6_chunked_flag(st);
+    if (flag != nullptr) {
+        RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA,
+                     "wkv6state_forward_saved: clearing the device flags failed");
+        const int rc = wkv6_l32_forward(B, T, H, r, k, v, w, 1, u, s0, sk, y, sT, static_cast<float*>(saved), flag, st, 1);
+        if (rc < 0) return rc;
+        if (rc == 0) {
+            // flagged units: the general-shape kernel redoes them; the flags travel with the saved states
+            wkv6_forward_kernel<bf16, 64><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, 1,
+                                                               (const bf16*)u, s0, sk, (bf16*)y, sT, flag);
+            if (int e = check_launch("wkv6state_forward_saved")) return e;
+            char* tail = static_cast<char*>(saved) + rwkvb200_wkv6_scratch_bytes(B, T, C) - sizeof(int) * kChunkedFlagUnits;
+            RWKV_REQUIRE(cudaMemcpyAsync(tail, flag, sizeof(int) * kChunkedFlagUnits, cudaMemcpyDeviceToDevice, st) == cudaSuccess,
+                         RWKVB200_ECUDA, "wkv6state_forward_saved: saving the device flags failed");
+            return RWKVB200_OK;
+        }
+    }
+    const int e = dtype == RWKVB200_F32
+                      ? launch_fwd<float>(B, T, C, H, r, k, v, w, 1, u, s0, sk, y, sT, st, "wkv6state_forward_saved")
+                      : launch_fwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, sk, y, sT, st, "wkv6state_forward_saved");
+    return e ? e : 1;
+}
+
+extern "C" int rwkvb200_wkv6state_backward_saved(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                                 const void* v, const void* w, const void* u, const float* s0,
+                                                 const void* gy, const float* dsT, void* gr, void* gk, void* gv,
+                                                 void* gw, void* gu, float* ds0, void* saved, int saved_valid, void* stream) {
+    if (int e = check_dims("wkv6state_backward_saved", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(gy);
+    RWKV_NOTNULL(gr); RWKV_NOTNULL(gk); RWKV_NOTNULL(gv); RWKV_NOTNULL(gw); RWKV_NOTNULL(gu); RWKV_NOTNULL(saved);
+    const int N = C / H, sk = s0 ? kF32 : kNone, dk = ds0 ? kF32 : kNone;
+    cudaStream_t st = as_stream(stream);
+    int* flag = nullptr;
+    if (saved_valid && dtype == RWKVB200_BF16 && chunked_ok<bf16>(T, N, {r, k, v, w, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0, saved}))
+        flag = wkv6_chunked_flag(st);
+    if (flag != nullptr) {
+        const char* tail = static_cast<const char*>(saved) + rwkvb200_wkv6_scratch_bytes(B, T, C) - sizeof(int) * kChunkedFlagUnits;
+        RWKV_REQUIRE(cudaMemcpyAsync(flag, tail, sizeof(int) * kChunkedFlagUnits, cudaMemcpyDeviceToDevice, st) == cudaSuccess,
+                     RWKVB200_ECUDA, "wkv6state_backward_saved: restoring the device flags failed");
+        if (int e = wkv6_l32_backward(B, T, H, r, k, v, w, 1, u, gy, dsT, static_cast<const float*>(saved), gr, gk, gv, gw, gu, ds0, dk, st))
+            return e;
+        // flagged units: the general-shape kernel redoes them (it uses the front of `saved` as its scratch, after
+        // the kernel above has read the states)
+        wkv6_backward_kernel<bf16, 64><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, 1,
+                                                            (const bf16*)u, s0, sk, (const bf16*)gy, dsT, (bf16*)gr, (bf16*)gk,
+                                                            (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0, dk, static_cast<float*>(saved), flag);
+        return check_launch("wkv6state_backward_saved");
+    }
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float>(B, T, C, H, r, k, v, w, 1, u, s0, sk, gy, dsT, gr, gk, gv, gw, gu, ds0, dk, saved, st, "wkv6state_backward_saved")
+               : launch_bwd<bf16>(B, T, C, H, r, k, v, w, 1, u, s0, sk, gy, dsT, gr, gk, gv, gw, gu, ds0, dk, saved, st, "wkv6state_backward_saved");
+}
+
 extern "C" int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const void* r, const void* k,
                                               const void* v, const void* w, const void* u, const float* s0,
                                               const void* gy, const float* dsT, void* gr, void* gk, void* gv,

@@ -178,22 +178,24 @@ class WKV_6STATE_EX(torch.autograd.Function):
             H = u.shape[0]
             ctx.dims = (B, T, C, H)
             r, k, v, w, u, s0 = (x.contiguous() for x in (r, k, v, w, u, s0))
-            ctx.save_for_backward(r, k, v, w, u, s0)
             y = torch.empty((B, T, C), device=r.device, dtype=r.dtype)
             sT = torch.empty_like(s0)
-            ops.wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT)
+            # the chunk-start states are kept for the backward (half the size of its scratch buffer is used)
+            saved = torch.empty(ops.wkv6_saved_bytes(B, T, C), dtype=torch.uint8, device=r.device)
+            ctx.saved_valid = ops.wkv6state_forward_saved(B, T, C, H, r, k, v, w, u, s0, y, sT, saved)
+            ctx.save_for_backward(r, k, v, w, u, s0, saved)
             return y, sT
 
     @staticmethod
     def backward(ctx, gy, dsT):
         with torch.no_grad():
             B, T, C, H = ctx.dims
-            r, k, v, w, u, s0 = ctx.saved_tensors
+            r, k, v, w, u, s0, saved = ctx.saved_tensors
             gr, gk, gv, gw = (torch.empty((B, T, C), device=gy.device, dtype=r.dtype) for _ in range(4))
             gu = torch.empty((B, C), device=gy.device, dtype=r.dtype)
             ds0 = torch.empty_like(s0)
-            ops.wkv6state_backward_ex(B, T, C, H, r, k, v, w, u, s0, gy.contiguous(), dsT.contiguous(), gr, gk, gv,
-                                      gw, gu, ds0)
+            ops.wkv6state_backward_saved(B, T, C, H, r, k, v, w, u, s0, gy.contiguous(), dsT.contiguous(), gr, gk, gv,
+                                         gw, gu, ds0, saved, ctx.saved_valid)
             return gr, gk, gv, gw, torch.sum(gu.float(), 0).view(H, C // H).to(u.dtype), ds0
 
 

@@ -258,6 +258,33 @@ def wkv6state_forward_ex(B, T, C, H, r, k, v, w, u, s0, y, sT):
              _ptr(s0, "s0", f), _ptr(y, "y", d), _ptr(sT, "sT", f), _stream(r))
 
 
+def wkv6state_forward_saved(B, T, C, H, r, k, v, w, u, s0, y, sT, saved):
+    """Forward that also leaves the chunk-start states in `saved` (uint8 tensor of wkv6_saved_bytes(B,T,C) bytes) for
+    wkv6state_backward_saved; returns True when they were saved (pass it on as `valid`)."""
+    d, f = r.dtype, torch.float32
+    with _dev(r, "r"):
+        rc = _lib.lib().rwkvb200_wkv6state_forward_saved(_dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v, w=w, u=u),
+                                                         _ptr(s0, "s0", f), _ptr(y, "y", d), _ptr(sT, "sT", f),
+                                                         saved.data_ptr(), _stream(r))
+        if rc < 0:
+            L = _lib.lib()
+            raise _lib.RwkvB200Error(f"rwkvb200_wkv6state_forward_saved: {L.rwkvb200_strerror(rc).decode()} ({rc}): "
+                                     f"{L.rwkvb200_last_error().decode()}")
+        return rc == 0
+
+
+def wkv6state_backward_saved(B, T, C, H, r, k, v, w, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0, saved, valid):
+    d, f = r.dtype, torch.float32
+    with _dev(r, "r"):
+        call("rwkvb200_wkv6state_backward_saved", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v, w=w, u=u),
+             _ptr(s0, "s0", f), _ptr(gy, "gy", d), _ptr(dsT, "dsT", f),
+             *_ptrs(d, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu), _ptr(ds0, "ds0", f), saved.data_ptr(), 1 if valid else 0, _stream(r))
+
+
+def wkv6_saved_bytes(B, T, C):
+    return _lib.lib().rwkvb200_wkv6_scratch_bytes(B, T, C)
+
+
 def tsplit_segments(B, T, H, device):
     """How many time segments the split forward should use for this launch: 1 unless the launch has at most a
     quarter as many (batch, head) units as the GPU has SMs (the unsplit tcgen05 forward walks a unit's chunks at
