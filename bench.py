@@ -327,8 +327,15 @@ def run_secondary(op, args):
         eew = torch.exp(ew)
         y, gr, gk, gv = (torch.empty(B, T, C, dtype=bf, device=dev) for _ in range(4))
         gw, gu = torch.empty(B, C, dtype=bf, device=dev), torch.empty(B, C, dtype=bf, device=dev)
-        fwd = lambda: R.ops.wkv5_forward(B, T, C, H, r, k, v, eew, u, y)
-        bwd = lambda: R.ops.wkv5_backward(B, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu)
+        # the training flow: the forward keeps the chunk-start states for the backward
+        saved5 = torch.empty(R.ops.wkv5_saved_bytes(B, T, C), dtype=torch.uint8, device=dev)
+        valid5 = [False]
+
+        def fwd():
+            valid5[0] = R.ops.wkv5_forward_saved(B, T, C, H, r, k, v, eew, u, y, saved5)
+
+        def bwd():
+            R.ops.wkv5_backward_saved(B, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu, saved5, valid5[0])
         bytes_f, bytes_b = 8 * C * B * T, 14 * C * B * T
         bound, note = "hbm", "chunked tensor-core kernels (mma.sync TF32), decay constant over time"
         Tc = 256

@@ -193,6 +193,15 @@ int rwkvb200_wkv6state_backward_ex(int dtype, int B, int T, int C, int H, const 
                                    void* gk, void* gv, void* gw, void* gu, float* ds0,
                                    void* scratch, void* stream);
 
+/* RWKV-5 training flow with saved states, as rwkvb200_wkv6state_forward_saved below: `saved` has
+ * rwkvb200_wkv5_scratch_bytes(B,T,C) bytes; gw32 / gu32 (optional, both or none): the unrounded fp32 (B,C) partials. */
+int rwkvb200_wkv5_forward_saved(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                const void* v, const float* w, const void* u, void* y, void* saved, void* stream);
+int rwkvb200_wkv5_backward_saved(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                 const void* v, const float* w, const float* ww, const void* u,
+                                 const void* gy, void* gr, void* gk, void* gv, void* gw, void* gu,
+                                 float* gw32, float* gu32, void* saved, int saved_valid, void* stream);
+
 /* RWKV-6 with fp32 state, training flow with saved states: the forward leaves the states at the start of every
  * 32-token chunk in `saved` (rwkvb200_wkv6_scratch_bytes(B,T,C) bytes of device memory, kept by the caller until the
  * backward), so that the backward need not run over the sequence once more to rebuild them.  The forward returns

@@ -411,6 +411,72 @@ extern "C" int rwkvb200_wkv5_backward_ws32(int dtype, int B, int T, int C, int H
                                          gw, gu, nullptr, nullptr, as_stream(stream), scratch, gw32, gu32);
 }
 
+// Training flow with saved states (see rwkvb200_wkv6state_forward_saved): the forward leaves the states at the start
+// of every 32-token chunk and the flags of its units in `saved` (rwkvb200_wkv5_scratch_bytes(B,T,C) bytes), the
+// backward uses them.  The forward returns RWKVB200_OK when it saved them, 1 when not (pass saved_valid = 0).
+// The backward also returns the unrounded fp32 (B,C) partials of gw and gu when gw32 / gu32 are given (both or none).
+extern "C" int rwkvb200_wkv5_forward_saved(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                           const void* v, const float* w, const void* u, void* y, void* saved, void* stream) {
+    if (int e = check_dims("wkv5_forward_saved", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(u); RWKV_NOTNULL(y); RWKV_NOTNULL(saved);
+    const int N = C / H;
+    cudaStream_t st = as_stream(stream);
+    int* flag = nullptr;
+    if (dtype == RWKVB200_BF16 && wkv6_forward_choice() && chunked_ok<bf16>(T, N, {r, k, v, u, y, saved})) flag = wkv6_chunked_flag(st);
+    if (flag != nullptr) {
+        RWKV_REQUIRE(cudaMemsetAsync(flag, 0, sizeof(int) * kChunkedFlagUnits, st) == cudaSuccess, RWKVB200_ECUDA,
+                     "wkv5_forward_saved: clearing the device flags failed");
+        const int rc = wkv6_l32_forward(B, T, H, r, k, v, w, 2, u, nullptr, 0, y, nullptr, static_cast<float*>(saved), flag, st, 1);
+        if (rc < 0) return rc;
+        if (rc == 0) {
+            wkv5_forward_kernel<bf16, 64, false><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w,
+                                                                      (const bf16*)u, nullptr, nullptr, (bf16*)y, flag);
+            if (int e = check_launch("wkv5_forward_saved")) return e;
+            char* tail = static_cast<char*>(saved) + rwkvb200_wkv5_scratch_bytes(B, T, C) - sizeof(int) * kChunkedFlagUnits;
+            RWKV_REQUIRE(cudaMemcpyAsync(tail, flag, sizeof(int) * kChunkedFlagUnits, cudaMemcpyDeviceToDevice, st) == cudaSuccess,
+                         RWKVB200_ECUDA, "wkv5_forward_saved: saving the device flags failed");
+            return RWKVB200_OK;
+        }
+    }
+    const int e = dtype == RWKVB200_F32 ? launch_fwd<float, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, st)
+                                        : launch_fwd<bf16, false>(B, T, C, H, r, k, v, w, u, nullptr, nullptr, y, st);
+    return e ? e : 1;
+}
+
+extern "C" int rwkvb200_wkv5_backward_saved(int dtype, int B, int T, int C, int H, const void* r, const void* k,
+                                            const void* v, const float* w, const float* ww, const void* u, const void* gy,
+                                            void* gr, void* gk, void* gv, void* gw, void* gu, float* gw32, float* gu32,
+                                            void* saved, int saved_valid, void* stream) {
+    if (int e = check_dims("wkv5_backward_saved", dtype, B, T, C, H)) return e;
+    RWKV_NOTNULL(r); RWKV_NOTNULL(k); RWKV_NOTNULL(v); RWKV_NOTNULL(w); RWKV_NOTNULL(ww); RWKV_NOTNULL(u);
+    RWKV_NOTNULL(gy); RWKV_NOTNULL(gr); RWKV_NOTNULL(gk); RWKV_NOTNULL(gv); RWKV_NOTNULL(gw); RWKV_NOTNULL(gu); RWKV_NOTNULL(saved);
+    RWKV_REQUIRE((gw32 == nullptr) == (gu32 == nullptr), RWKVB200_EINVAL, "wkv5_backward_saved: gw32 and gu32 go together");
+    const int N = C / H;
+    cudaStream_t st = as_stream(stream);
+    int* flag = nullptr;
+    if (saved_valid && dtype == RWKVB200_BF16 && chunked_ok<bf16>(T, N, {r, k, v, u, gy, gr, gk, gv, gw, gu, saved})) flag = wkv6_chunked_flag(st);
+    if (flag != nullptr) {
+        const char* tail = static_cast<const char*>(saved) + rwkvb200_wkv5_scratch_bytes(B, T, C) - sizeof(int) * kChunkedFlagUnits;
+        RWKV_REQUIRE(cudaMemcpyAsync(flag, tail, sizeof(int) * kChunkedFlagUnits, cudaMemcpyDeviceToDevice, st) == cudaSuccess,
+                     RWKVB200_ECUDA, "wkv5_backward_saved: restoring the device flags failed");
+        if (int e = wkv6_l32_backward(B, T, H, r, k, v, ww, 3, u, gy, nullptr, static_cast<const float*>(saved), gr, gk, gv, gw, gu,
+                                      nullptr, 0, st, gw32, gu32))
+            return e;
+        wkv5_backward_kernel<bf16, 64, false><<<B * H, 64, 0, st>>>(T, C, H, N, (const bf16*)r, (const bf16*)k, (const bf16*)v, w, ww,
+                                                                   (const bf16*)u, nullptr, nullptr, nullptr, (const bf16*)gy,
+                                                                   (bf16*)gr, (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, nullptr,
+                                                                   nullptr, flag);
+        if (gw32 != nullptr)
+            widen_partials_kernel<bf16><<<(B * C + 255) / 256, 256, 0, st>>>(B * C, C, N, (const bf16*)gw, (const bf16*)gu, gw32, gu32, flag);
+        return check_launch("wkv5_backward_saved");
+    }
+    return dtype == RWKVB200_F32
+               ? launch_bwd<float, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv, gw, gu, nullptr,
+                                          nullptr, st, saved, gw32, gu32)
+               : launch_bwd<bf16, false>(B, T, C, H, r, k, v, w, ww, u, nullptr, nullptr, nullptr, gy, gr, gk, gv, gw, gu, nullptr,
+                                         nullptr, st, saved, gw32, gu32);
+}
+
 extern "C" int rwkvb200_wkv5a_forward(int dtype, int B, int T, int C, int H, const void* r, const void* k,
                                       const void* v, const float* w1, const void* u1, const float* w2,
                                       const void* u2, void* y, void* stream) {

@@ -64,22 +64,25 @@ class WKV_5(torch.autograd.Function):
             r, k, v, w, u = (x.contiguous() for x in (r, k, v, w, u))
             ew = (-torch.exp(w.float())).contiguous()
             eew = torch.exp(ew).contiguous()
-            ctx.save_for_backward(r, k, v, eew, ew, u)
             y = torch.empty((B, T, C), device=r.device, dtype=r.dtype)
-            ops.wkv5_forward(B, T, C, H, r, k, v, eew, u, y)
+            # the chunk-start states are kept for the backward (no second pass over the sequence there)
+            saved = torch.empty(ops.wkv5_saved_bytes(B, T, C), dtype=torch.uint8, device=r.device)
+            ctx.saved_valid = ops.wkv5_forward_saved(B, T, C, H, r, k, v, eew, u, y, saved)
+            ctx.save_for_backward(r, k, v, eew, ew, u, saved)
             return y
 
     @staticmethod
     def backward(ctx, gy):
         with torch.no_grad():
             B, T, C, H = ctx.B, ctx.T, ctx.C, ctx.H
-            r, k, v, eew, ew, u = ctx.saved_tensors
+            r, k, v, eew, ew, u, saved = ctx.saved_tensors
             gr, gk, gv = (torch.empty((B, T, C), device=gy.device, dtype=r.dtype) for _ in range(3))
             gw, gu = (torch.empty((B, C), device=gy.device, dtype=r.dtype) for _ in range(2))
             # the harness sums bf16 (B,C) partials in bf16 (wkv5_bf16/run.py:83-87); here the unrounded fp32
             # partials are summed in fp32 on the device and rounded once
             gw32, gu32 = (torch.empty((B, C), device=gy.device, dtype=torch.float32) for _ in range(2))
-            ops.wkv5_backward(B, T, C, H, r, k, v, eew, ew, u, gy.contiguous(), gr, gk, gv, gw, gu, gw32, gu32)
+            ops.wkv5_backward_saved(B, T, C, H, r, k, v, eew, ew, u, gy.contiguous(), gr, gk, gv, gw, gu, saved,
+                                    ctx.saved_valid, gw32, gu32)
             sums = torch.empty((2, C), device=gy.device, dtype=torch.float32)
             ops.reduce_batch_partials(gw32, sums[0])
             ops.reduce_batch_partials(gu32, sums[1])

@@ -152,6 +152,32 @@ def wkv5_backward(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu, gw32=No
                  _ptr(gu32, "gu32", torch.float32), sc.data_ptr(), _stream(r))
 
 
+def wkv5_saved_bytes(B, T, C):
+    return _lib.lib().rwkvb200_wkv5_scratch_bytes(B, T, C)
+
+
+def wkv5_forward_saved(B, T, C, H, r, k, v, w, u, y, saved):
+    """Forward that also leaves the chunk-start states in `saved` (uint8 tensor of wkv5_saved_bytes(B,T,C) bytes) for
+    wkv5_backward_saved; returns True when they were saved (pass it on as `valid`)."""
+    d = r.dtype
+    with _dev(r, "r"):
+        L = _lib.lib()
+        rc = L.rwkvb200_wkv5_forward_saved(_dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v), _ptr(w, "w", torch.float32),
+                                           _ptr(u, "u", d), _ptr(y, "y", d), saved.data_ptr(), _stream(r))
+        if rc < 0:
+            raise _lib.RwkvB200Error(f"rwkvb200_wkv5_forward_saved: {L.rwkvb200_strerror(rc).decode()} ({rc}): "
+                                     f"{L.rwkvb200_last_error().decode()}")
+        return rc == 0
+
+
+def wkv5_backward_saved(B, T, C, H, r, k, v, w, ww, u, gy, gr, gk, gv, gw, gu, saved, valid, gw32=None, gu32=None):
+    d, f = r.dtype, torch.float32
+    with _dev(r, "r"):
+        call("rwkvb200_wkv5_backward_saved", _dt(r, "r"), B, T, C, H, *_ptrs(d, r=r, k=k, v=v),
+             _ptr(w, "w", f), _ptr(ww, "ww", f), *_ptrs(d, u=u, gy=gy, gr=gr, gk=gk, gv=gv, gw=gw, gu=gu),
+             _ptr(gw32, "gw32", f), _ptr(gu32, "gu32", f), saved.data_ptr(), 1 if valid else 0, _stream(r))
+
+
 def reduce_batch_partials(partial, out):
     """out (n,) fp32 <- sum over dim 0 of partial (B, n) (bf16 or fp32), accumulated in fp32."""
     B = partial.shape[0]

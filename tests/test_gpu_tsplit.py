@@ -272,3 +272,35 @@ def test_rwkv6_saved_states_flow(R, B, T, H, shift):
         if name == "gw" and shift > 0:
             continue   # e^2 and more per token: the decay gradient is below what bf16 inputs resolve
         Hh.assert_close(x, want, Hh.TOL_BF16, f"{name} (saved-states flow)")
+
+
+@pytest.mark.parametrize("B,T,H,hi", [(2, 256, 3, -1.0), (1, 48, 2, -1.0), (2, 64, 2, 2.5)])
+def test_rwkv5_saved_states_flow(R, B, T, H, hi):
+    """RWKV-5: forward that keeps the chunk-start states + backward that uses them, with the fp32 partials of the
+    parameter gradients, against the oracle (hi = 2.5: decays too strong for the chunked form in some channels)."""
+    N = 64
+    C = H * N
+    g = Hh.gen(51)
+    r, k, v = (0.5 * Hh.randn(g, B, T, C) for _ in range(3))
+    w_raw, u, gy = Hh.rand(g, H, N, lo=-6 if hi < 0 else -1, hi=hi), Hh.rand(g, H, N, lo=-1, hi=1), Hh.randn(g, B, T, C)
+    xs = [x.to(BF).double().requires_grad_(True) for x in (r, k, v, w_raw, u)]
+    yo = O.wkv5(*xs, H)
+    yo.backward(gy.to(BF).double())
+    rd, kd, vd, ud, gd = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, u, gy))
+    ew = -torch.exp(w_raw.to(BF).float()).to(DEV).contiguous()
+    eew = torch.exp(ew).contiguous()
+    nan = float("nan")
+    y = torch.full((B, T, C), nan, dtype=BF, device=DEV)
+    saved = torch.empty(R.ops.wkv5_saved_bytes(B, T, C), dtype=torch.uint8, device=DEV)
+    valid = R.ops.wkv5_forward_saved(B, T, C, H, rd, kd, vd, eew, ud, y, saved)
+    assert valid
+    gr, gk, gv = (torch.full((B, T, C), nan, dtype=BF, device=DEV) for _ in range(3))
+    gw, gu = torch.full((B, C), nan, dtype=BF, device=DEV), torch.full((B, C), nan, dtype=BF, device=DEV)
+    gw32, gu32 = torch.full((B, C), nan, device=DEV), torch.full((B, C), nan, device=DEV)
+    R.ops.wkv5_backward_saved(B, T, C, H, rd, kd, vd, eew, ew, ud, gd, gr, gk, gv, gw, gu, saved, valid, gw32, gu32)
+    torch.cuda.synchronize()
+    got = (y, gr, gk, gv, gw32.sum(0), gu32.sum(0))
+    for x, want, name in zip(got, [yo.detach()] + [xx.grad for xx in xs], ("y", "gr", "gk", "gv", "gw", "gu")):
+        assert torch.isfinite(x.float()).all(), name
+        Hh.assert_close(x, want, Hh.TOL_BF16, f"{name} (RWKV-5 saved-states flow)")
+    Hh.assert_close(gw.float().sum(0), xs[3].grad, Hh.TOL_BF16, "gw from the bf16 partials")
