@@ -428,12 +428,14 @@ def run_wkv5_sharded(args, rank, world, local):
     y, gr, gk, gv = (torch.empty(bl, T, C, dtype=bf, device=dev) for _ in range(4))
     gw, gu = torch.empty(bl, C, dtype=bf, device=dev), torch.empty(bl, C, dtype=bf, device=dev)
     red = R.dist.ParamGradReducer(dev, 2 * C)
+    gw32, gu32 = torch.empty(bl, C, device=dev), torch.empty(bl, C, device=dev)   # unrounded partials of gw, gu
+    saved = torch.empty(R.ops.wkv5_saved_bytes(bl, T, C), dtype=torch.uint8, device=dev)
 
     def step():
-        R.ops.wkv5_forward(bl, T, C, H, r, k, v, eew, u, y)
-        R.ops.wkv5_backward(bl, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu)
+        valid = R.ops.wkv5_forward_saved(bl, T, C, H, r, k, v, eew, u, y, saved)
+        R.ops.wkv5_backward_saved(bl, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu, saved, valid, gw32, gu32)
         red.reset()
-        red.add(gw); red.add(gu)
+        red.add(gw32); red.add(gu32)
         red.launch()
         return red.result(0), red.result(1)
 
@@ -450,7 +452,7 @@ def run_wkv5_sharded(args, rank, world, local):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     # the same reduction on one rank over the whole batch would be sum over all rows: check the collective
     chk = torch.stack([gws.sum(), gus.sum()]).double()
-    loc = torch.stack([gw.float().sum(), gu.float().sum()]).double()
+    loc = torch.stack([gw32.sum(), gu32.sum()]).double()   # local sums of the unrounded partials
     dist.all_reduce(loc, op=dist.ReduceOp.SUM)
     if rank == 0:
         ms = t.item() / args.steps
