@@ -68,7 +68,8 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                       const void* __restrict__ w_, const bf16* __restrict__ u_, const bf16* __restrict__ gy_,
                       const float* __restrict__ dsT_, const float* __restrict__ ck_, bf16* __restrict__ gr_,
                       bf16* __restrict__ gk_, bf16* __restrict__ gv_, bf16* __restrict__ gw_, bf16* __restrict__ gu_,
-                      void* __restrict__ ds0_, int ds0_kind, float* __restrict__ gw32_, float* __restrict__ gu32_) {
+                      void* __restrict__ ds0_, int ds0_kind, float* __restrict__ gw32_, float* __restrict__ gu32_,
+                      const __grid_constant__ TileMaps<5> maps) {
     constexpr bool kStatic = WMODE >= 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -166,6 +167,15 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
     };
     fetch(nchunks - 1);
+    // two chunks ahead, into L2: the tiles of r, k, v, gy (and of a bf16 per-token decay) and the chunk-start state
+    auto ask_l2 = [&](int c) {
+        if (tid != 224 || !maps.valid) return;
+#pragma unroll
+        for (int q = 0; q < (WMODE == 1 ? 5 : 4); ++q) l2_prefetch_tile(&maps.m[q], hh * 64, bb * T + c * LC);
+        const float* sp = ck + (i64)c * 64 * 64;
+        if ((reinterpret_cast<uintptr_t>(sp) & 15) == 0) l2_prefetch(sp, 64 * 64 * 4);
+    };
+    if (nchunks > 1) ask_l2(nchunks - 2);
     int fail = 0;
     uint32_t par = 0;
     float gu_acc[2] = {0.f, 0.f}, gw_acc[2] = {0.f, 0.f};   // sums over this thread's tokens (gw only for a static decay)
@@ -249,6 +259,7 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tmem_wait_st();
         }
         if (c > 0) fetch(c - 1);
+        if (c > 1) ask_l2(c - 2);
         if (!mbar_wait(bar, par)) fail = 1;
         tc_fence_after();
         // ---- 3. A and G masked into shared memory; this warp: rows of its quarter, columns 16*hs .. 16*hs+15 ---
@@ -486,6 +497,9 @@ int wkv6_l32_backward(int B, int T, int H, const void* r, const void* k, const v
                       const void* gy, const float* dsT, const float* ck, void* gr, void* gk, void* gv, void* gw, void* gu,
                       void* ds0, int ds0_kind, cudaStream_t st, float* gw32, float* gu32) {
     using namespace v6b;
+    TileMaps<5> maps;
+    const void* in[5] = {r, k, v, gy, w_mode == 1 ? w : r};
+    make_tile_maps<5>(maps, in, B, T, H);
     dim3 grid(H, B);
 #define RWKV_GO(M)                                                                                                        \
     do {                                                                                                                  \
@@ -494,7 +508,7 @@ int wkv6_l32_backward(int B, int T, int H, const void* r, const void* k, const v
         wkv6b_backward_kernel<M><<<grid, BNT, Smem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)k, (const bf16*)v, w,  \
                                                                  (const bf16*)u, (const bf16*)gy, dsT, ck, (bf16*)gr,    \
                                                                  (bf16*)gk, (bf16*)gv, (bf16*)gw, (bf16*)gu, ds0,        \
-                                                                 ds0_kind, gw32, gu32);                                  \
+                                                                 ds0_kind, gw32, gu32, maps);                            \
     } while (0)
     switch (w_mode) {
         case 0: RWKV_GO(0); break;

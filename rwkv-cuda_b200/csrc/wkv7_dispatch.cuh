@@ -32,6 +32,10 @@ int wkv7_l32_bwdp_error(int clear);
 int wkv7_l32_forward_pipelined(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k, const void* v,
                                const void* a, const void* b, void* y, float* sT, float* s, cudaStream_t st);
 int wkv7_l32_fwdp_error(int clear);
+// A tensor map over a (rows, cols) bf16 tensor with a box of [32 rows][64 columns] (one chunk of one head), made with
+// cuTensorMapEncodeTiled obtained through the runtime; false when the driver has no such entry point or refuses
+// the shape or the alignment.  `map` points at a CUtensorMap (128 bytes, 64-byte aligned).
+bool wkv7_make_tile_map(void* map, const void* base, unsigned long long rows, unsigned long long cols);
 // sticky per-device status words of the two kernels (0 = fine) and their reset
 int wkv7_l32_fwd_error();
 int wkv7_l32_bwd_error();

@@ -93,7 +93,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                       const bf16* __restrict__ b_, const bf16* __restrict__ dy_, const float* __restrict__ dsT_,
                       const float* __restrict__ ck_, float* __restrict__ ds0_, bf16* __restrict__ dr_,
                       bf16* __restrict__ dw_, bf16* __restrict__ dk_, bf16* __restrict__ dv_, bf16* __restrict__ da_,
-                      bf16* __restrict__ db_) {
+                      bf16* __restrict__ db_, const __grid_constant__ TileMaps<7> maps) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // the swizzle acts on address bits
     unsigned char *AR = smem + BwdSmemX::kAR, *BK = smem + BwdSmemX::kBK, *SV = smem + BwdSmemX::kSV, *EY = smem + BwdSmemX::kEY;
@@ -167,6 +167,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
     RawChunk<7, BTPW> raw;
     fetch_chunk<7, BTPW>(raw, src, tok0, C, nchunks - 1, T, warp, lane);
+    if (nchunks > 1 && tid == 224) prefetch_chunk_l2<7>(maps, hh * 64, bb * T + (nchunks - 2) * LC, ck + (i64)(nchunks - 2) * 64 * 64, 64 * 64 * 4);
     int fail = 0;
     uint32_t par = 0;
     ChainSync cs{bar + 6, 0, 0};   // used by warp 0 only
@@ -247,6 +248,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tmem_wait_st();
         }
         if (c > 0) fetch_chunk<7, BTPW>(raw, src, tok0, C, c - 1, T, warp, lane);   // under the chain
+        if (c > 1 && tid == 224) prefetch_chunk_l2<7>(maps, hh * 64, bb * T + (c - 2) * LC, ck + (i64)(c - 2) * 64 * 64, 64 * 64 * 4);   // the one after into L2
         WKV7_PHASE(5);   // issue of the forward part, decay scaling of E, request of the next chunk
         if (!mbar_wait(bar + 1, par)) fail = 2;
         tc_fence_after();
@@ -512,11 +514,14 @@ int wkv7_l32_backward(int B, int T, int H, const void* r, const void* w, const v
     using namespace v7x;
     cudaError_t e = cudaFuncSetAttribute(wkv7x_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmemX::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv7_backward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    TileMaps<7> maps;
+    const void* in[7] = {r, w, k, v, a, b, dy};
+    make_tile_maps<7>(maps, in, B, T, H);
     dim3 grid(H, B);
     wkv7x_backward_kernel<<<grid, BNT, BwdSmemX::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)w, (const bf16*)k,
                                                                (const bf16*)v, (const bf16*)a, (const bf16*)b, (const bf16*)dy,
                                                                dsT, s, ds0, (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv,
-                                                               (bf16*)da, (bf16*)db);
+                                                               (bf16*)da, (bf16*)db, maps);
     return check_launch("wkv7_backward(tcgen05, 32-token chunks)");
 }
 

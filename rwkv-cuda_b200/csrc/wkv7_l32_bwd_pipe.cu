@@ -70,6 +70,19 @@ static_assert(PipeSmem::kBytes <= 232448, "fits the shared memory of one SM");
 
 __device__ int g_l32_bwdp_error = 0;
 
+// Tensors X0 .. X1-1 of a thread's part of chunk c (fetch_chunk in pieces: a burst of 28 four-byte loads per
+// thread from all warps at once takes 1.3 k cycles to issue, so the pieces go where the warps would wait anyway).
+template <int X0, int X1>
+__device__ __forceinline__ void fetch_part(RawChunk<7, 4>& rc, const bf16* const* src, i64 tok0, int C, int c, int T, int warp, int lane) {
+    const int t0 = c * LC + 4 * warp;
+    const i64 off = tok0 + (i64)t0 * C + 2 * lane;
+#pragma unroll
+    for (int x = X0; x < X1; ++x)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            rc.x[x][q] = (t0 + q < T) ? __ldg(reinterpret_cast<const unsigned int*>(src[x] + off + (i64)q * C)) : 0u;
+}
+
 __device__ __forceinline__ void scatter_u_half(const float (*u)[4], int quarter, int hs, int lane, float* Uab, unsigned char* N1,
                                                unsigned char* Uak, unsigned char* Ubr, unsigned char* Ukr) {
     const int g = lane >> 2, t = lane & 3;
@@ -101,9 +114,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// mbarriers: 0-1 full[set], 2-3 empty[set] (one arrival each); front: 4 U, 5 SA, 6 its chain; back: 7 EV,
-// 8 P, 9 E/ET, 10 gradients, 11 its chain
-enum { kFull = 0, kEmpty = 2, kFU = 4, kFSA = 5, kFChain = 6, kBEV = 7, kBP = 8, kBE = 9, kBG = 10, kBChain = 11, kNBar = 12 };
+// mbarriers: 0-1 full[set], 2-3 empty[set] (one arrival each); front: 4 U, 5-6 SA[set], 7 its chain; back: 8 EV,
+// 9 P, 10 E/ET, 11 gradients, 12 its chain
+enum { kFull = 0, kEmpty = 2, kFU = 4, kFSA = 5, kFChain = 7, kBEV = 8, kBP = 9, kBE = 10, kBG = 11, kBChain = 12, kNBar = 13 };
 
 __global__ void __launch_bounds__(PNT, 1)
 wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ w_,
@@ -152,7 +165,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     __syncthreads();
     tc_fence_after();
     const uint32_t tm0 = __shfl_sync(0xffffffffu, tmem_slot[0], 0);
-    const uint32_t tmE = tm0, tmET = tm0 + 64, tmW1 = tm0 + 128, tmW2 = tm0 + 192, tmF1 = tm0 + 256, tmF2 = tm0 + 320;
+    const uint32_t tmE = tm0, tmET = tm0 + 64, tmW1 = tm0 + 128, tmW2 = tm0 + 192, tmF1 = tm0 + 256, tmF2a = tm0 + 320, tmF2b = tm0 + 384;   // X_a / SA per set
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t lead = elect_one();
     const int gbar = 1 + grp;   // named barrier of this group
@@ -195,6 +208,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             float* Uab = reinterpret_cast<float*>(base + SetSmem::kUab);
             const uint32_t arA = smem_u32(AR), bkA = smem_u32(BK), svA = smem_u32(SV), s0A = smem_u32(S0);
             const uint32_t uakA = smem_u32(Uak), d0A = smem_u32(D0), n1A = smem_u32(N1);
+            const uint32_t tmF2 = set ? tmF2b : tmF2a;
             // the back group must have released this set (it was used two chunks ago)
             PIPE_MARK(1);
             if (it >= 2 && !mbar_wait(bar + kEmpty + set, ((it >> 1) - 1) & 1)) fail = 30;
@@ -234,6 +248,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int ks = 0; ks < 8; ++ks)   // X_a = S0 A~^T, needed after the inverse only
                     mma_ss(tmF2, desc_k(s0A, 0, ks * 8, HALF64), desc_k(arA, 0, ks * 8, HALF64), idesc64(32, 0, 0), ks > 0, lead);
             }
+            if (c > 0) fetch_part<0, 4>(raw, src, tok0, C, c - 1, T, wg, lane);   // the next chunk, first part: under U
             PIPE_MARK(2);
             if (!mbar_wait(bar + kFU, par)) fail = 31;
             PIPE_MARK(3);
@@ -257,30 +272,19 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int ks = 0; ks < 4; ++ks)   // Z = X_a + V U_ak
                     mma_ss(tmF2, desc_mn(svA + 32 * 128, ks * 8, HALF64), desc_mn(uakA, ks * 8, HALF32), idesc64(32, 1, 1), 1, lead);
                 cs.sync(lead);
-                issue_solve(tmF2 + 32, tmF2, d0A, n1A, lead, cs, []() {});   // SA = Z T
-                mma_commit(bar + kFSA, lead);
+                issue_solve(tmF2 + 32, tmF2, d0A, n1A, lead, cs, [&]() {   // SA = Z T
+                    if (c > 0) fetch_part<4, 7>(raw, src, tok0, C, c - 1, T, wg, lane);
+                });
+                mma_commit(bar + kFSA + set, lead);   // the back group takes SA out of tensor memory
                 if (cs.fail) fail = 32;
+            } else if (c > 0) {
+                fetch_part<4, 7>(raw, src, tok0, C, c - 1, T, wg, lane);   // the next chunk, second part: under the chain
             }
             PIPE_MARK(5);
-            if (c > 0) fetch_chunk<7, 4>(raw, src, tok0, C, c - 1, T, wg, lane);   // under the chain
-            if (!mbar_wait(bar + kFSA, par)) fail = 33;
-            tc_fence_after();
-            {   // SA -> SV rows 0-31 ([t][i]); this warp: tokens 16*hs .. 16*hs+15
-                float sa[2][4];
-                tmem_ld_tiles<2>(sa, tmF2 + 32 + 16 * hs + lane_off);
-                tmem_wait_ld();
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = row0 + g + ((e & 2) ? 8 : 0), tt = 16 * hs + nt * 8 + 2 * t + (e & 1);
-                        *reinterpret_cast<float*>(SV + sw(tt, i, HALF64)) = tf32rf(sa[nt][e]);
-                    }
-            }
             proxy_fence();
             tc_fence_before();
             group_sync(gbar, GNT);
-            if (gtid == 0) mbar_arrive(bar + kFull + set);   // the set is complete
+            if (gtid == 0) mbar_arrive(bar + kFull + set);   // the set is complete (but for SA, which the back group converts)
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
         // the outputs of the last two chunks (iterations nchunks-2 and nchunks-1 of the back group)
@@ -332,20 +336,16 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             group_sync(gbar, GNT);
             tc_fence_after();
             if (gabort[1]) break;
-            {   // Ew = E diag(We), ETw = diag(We) ET
-                float Ed[4][4], Td[4][4];
+            {   // Ew = E diag(We)  (ETw = diag(We) ET follows under the first products, which do not read it)
+                float Ed[4][4];
                 tmem_ld_tiles<4>(Ed, tmE + 32 * hs + lane_off);
-                tmem_ld_tiles<4>(Td, tmET + 32 * hs + lane_off);
                 tmem_wait_ld();
-                const float wr0 = We[row0 + g], wr1 = We[row0 + g + 8];
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const float2 wc = *reinterpret_cast<const float2*>(We + 32 * hs + nt * 8 + 2 * t);
                     Ed[nt][0] *= wc.x; Ed[nt][1] *= wc.y; Ed[nt][2] *= wc.x; Ed[nt][3] *= wc.y;
-                    Td[nt][0] *= wr0; Td[nt][1] *= wr0; Td[nt][2] *= wr1; Td[nt][3] *= wr1;
                 }
                 tmem_st_tiles<4>(tmE + 32 * hs + lane_off, Ed);
-                tmem_st_tiles<4>(tmET + 32 * hs + lane_off, Td);
                 tmem_wait_st();
             }
             tc_fence_before();
@@ -374,6 +374,32 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     mma_ts(tmW1 + 32, tmW1 + ks * 8, desc_k(uakA, 0, ks * 8, HALF32), idesc64(32, 0, 0), 1, lead);
                 mma_commit(bar + kBEV, lead);
                 if (cs.fail) fail = 41;
+            }
+            // meanwhile, under the chain: SA of this chunk (left in tensor memory by the front group) -> SV rows 0-31
+            // ([t][i]; this warp: tokens 16*hs .. 16*hs+15), and ETw = diag(We) ET; both are read by the products after EV only
+            if (!mbar_wait(bar + kFSA + set, (it >> 1) & 1)) fail = 46;
+            tc_fence_after();
+            {
+                float sa[2][4];
+                tmem_ld_tiles<2>(sa, (set ? tmF2b : tmF2a) + 32 + 16 * hs + lane_off);
+                tmem_wait_ld();
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = row0 + g + ((e & 2) ? 8 : 0), tt = 16 * hs + nt * 8 + 2 * t + (e & 1);
+                        *reinterpret_cast<float*>(SV + sw(tt, i, HALF64)) = tf32rf(sa[nt][e]);
+                    }
+            }
+            {
+                float Td[4][4];
+                tmem_ld_tiles<4>(Td, tmET + 32 * hs + lane_off);
+                tmem_wait_ld();
+                const float wr0 = We[row0 + g], wr1 = We[row0 + g + 8];
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) { Td[nt][0] *= wr0; Td[nt][1] *= wr0; Td[nt][2] *= wr1; Td[nt][3] *= wr1; }
+                tmem_st_tiles<4>(tmET + 32 * hs + lane_off, Td);
+                tmem_wait_st();
             }
             if (!mbar_wait(bar + kBEV, par)) fail = 42;
             tc_fence_after();

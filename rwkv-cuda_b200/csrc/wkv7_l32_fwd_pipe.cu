@@ -406,6 +406,10 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
 }
 }  // namespace
 
+bool wkv7_make_tile_map(void* map, const void* base, unsigned long long rows, unsigned long long cols) {
+    return encode_tiled() != nullptr && make_map(reinterpret_cast<CUtensorMap*>(map), base, rows, cols);
+}
+
 // Returns RWKVB200_OK, an error code, or 1 when tensor maps cannot be made here (no entry point in the driver, or a
 // shape it refuses): the caller then uses the one-group kernel.
 int wkv7_l32_forward_pipelined(int B, int T, int H, const float* s0, const void* r, const void* w, const void* k, const void* v,
