@@ -25,6 +25,11 @@ template <typename E> __device__ __forceinline__ E from_f(float x);
 template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
 
+// hint: bring the line that holds *p into L1 (ties up no register, unlike a load issued early)
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(__cvta_generic_to_global(p)));
+}
+
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
 // ---- error plumbing (host) ----------------------------------------------------------

@@ -26,6 +26,8 @@ struct __align__(16) Stage {
     float a[2][NMAX];
 };
 
+constexpr int kAhead = 8;   // tokens between the L1 request for a token's rows and their use
+
 template <typename E, int NMAX>
 __global__ void __launch_bounds__(NMAX) wkv7_forward_kernel(int T, int H, int N, int chunk, const float* __restrict__ s0_,
                                                            const E* __restrict__ r_, const E* __restrict__ w_,
@@ -45,6 +47,8 @@ __global__ void __launch_bounds__(NMAX) wkv7_forward_kernel(int T, int H, int N,
     const i64 base = (i64)bb * T * C + hh * N + i;
     float* ck = ck_ ? ck_ + (i64)(bb * H + hh) * (T / chunk) * N * N : nullptr;
 
+    // one thread per 128-byte line of a row of N elements asks for the rows of the token kAhead steps on
+    const bool line_lead = i == 0 || (reinterpret_cast<uintptr_t>(r_ + base) & 127) < sizeof(E);
     float rn = 0.f, wn = 0.f, kn = 0.f, vn = 0.f, an = 0.f, bn = 0.f;
     if (live) {
         rn = to_f(r_[base]); wn = to_f(w_[base]); kn = to_f(k_[base]);
@@ -53,7 +57,7 @@ __global__ void __launch_bounds__(NMAX) wkv7_forward_kernel(int T, int H, int N,
     for (int t = 0; t < T; ++t) {
         const int p = t & 1;
         rs.a[p][i] = rn;
-        ds.a[p][i] = live ? expf(kWScale / (1.f + expf(-wn))) : 0.f;
+        ds.a[p][i] = live ? __expf(kWScale * __fdividef(1.f, 1.f + __expf(-wn))) : 0.f;   // hardware exp2 / reciprocal: as the reference's build does
         ks.a[p][i] = kn; as.a[p][i] = an; bs.a[p][i] = bn;
         const float v = vn;
         __syncthreads();
@@ -62,12 +66,21 @@ __global__ void __launch_bounds__(NMAX) wkv7_forward_kernel(int T, int H, int N,
             rn = to_f(r_[o]); wn = to_f(w_[o]); kn = to_f(k_[o]);
             vn = to_f(v_[o]); an = to_f(a_[o]); bn = to_f(b_[o]);
         }
-        float sa = 0.f;
+        if (t + kAhead < T && live && line_lead) {   // the rows of a later token into L1: the loads above then find them there
+            const i64 o = base + (i64)(t + kAhead) * C;
+            prefetch_l1(r_ + o); prefetch_l1(w_ + o); prefetch_l1(k_ + o);
+            prefetch_l1(v_ + o); prefetch_l1(a_ + o); prefetch_l1(b_ + o);
+        }
+        float sa;
+        {   // four partial sums: one chain of NMAX dependent multiply-adds would be bound by their latency
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < NMAX; j += 4) {
-            const float4 a4 = *reinterpret_cast<const float4*>(&as.a[p][j]);
-            sa = fmaf(S[j], a4.x, sa); sa = fmaf(S[j + 1], a4.y, sa);
-            sa = fmaf(S[j + 2], a4.z, sa); sa = fmaf(S[j + 3], a4.w, sa);
+            for (int j = 0; j < NMAX; j += 4) {
+                const float4 a4 = *reinterpret_cast<const float4*>(&as.a[p][j]);
+                s0 = fmaf(S[j], a4.x, s0); s1 = fmaf(S[j + 1], a4.y, s1);
+                s2 = fmaf(S[j + 2], a4.z, s2); s3 = fmaf(S[j + 3], a4.w, s3);
+            }
+            sa = (s0 + s1) + (s2 + s3);
         }
         float y = 0.f;
 #pragma unroll
@@ -129,6 +142,8 @@ __global__ void __launch_bounds__(NMAX) wkv7_backward_kernel(
 
     const int C = H * N;
     const i64 base = (i64)bb * T * C + hh * N + i;
+    const bool line_lead = i == 0 || (reinterpret_cast<uintptr_t>(r_ + base) & 127) < sizeof(E);
+    const bool line_lead_sa = i == 0 || (reinterpret_cast<uintptr_t>(sa_ + base) & 127) < sizeof(float);
     float rn = 0.f, wn = 0.f, kn = 0.f, vn = 0.f, an = 0.f, bn = 0.f, gn = 0.f, sn = 0.f;
     if (live) {
         const i64 o = base + (i64)(T - 1) * C;
@@ -137,28 +152,33 @@ __global__ void __launch_bounds__(NMAX) wkv7_backward_kernel(
     }
     for (int t = T - 1; t >= 0; --t) {
         const int p = t & 1;
-        const float sig = 1.f / (1.f + expf(-wn));
-        const float di = live ? expf(kWScale * sig) : 1.f;
+        // hardware exp2 / reciprocal (as the reference's build does); the accurate forms cost the loop below its registers
+        const float sig = __fdividef(1.f, 1.f + __expf(-wn));
+        const float di = live ? __expf(kWScale * sig) : 1.f;
         const float ri = rn, ki = kn, ai = an, bi = bn, gi = gn;
         rs.a[p][i] = rn; ds.a[p][i] = live ? di : 0.f; ks.a[p][i] = kn; vs.a[p][i] = vn;
         as.a[p][i] = an; bs.a[p][i] = bn; gs.a[p][i] = gn; ss.a[p][i] = sn;
         __syncthreads();
-        if (t > 0 && live) {
-            const i64 o = base + (i64)(t - 1) * C;
-            rn = to_f(r_[o]); wn = to_f(w_[o]); kn = to_f(k_[o]); vn = to_f(v_[o]);
-            an = to_f(a_[o]); bn = to_f(b_[o]); gn = to_f(dy_[o]); sn = sa_[o];
-        }
         if ((t + 1) % chunk == 0 && live) {
             const float* src = ck + (i64)(t / chunk) * N * N + (i64)i * N;
 #pragma unroll
             for (int j = 0; j < NMAX; ++j)
                 if (j < N) ST[j] = src[j];
         }
-        float dr = 0.f;
+        float dr;
+        {   // four partial sums: one chain of NMAX dependent multiply-adds would be bound by their latency
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < NMAX; ++j) dr = fmaf(ST[j], gs.a[p][j], dr);
+            for (int j = 0; j < NMAX; j += 4) {
+                d0 = fmaf(ST[j], gs.a[p][j], d0);
+                d1 = fmaf(ST[j + 1], gs.a[p][j + 1], d1);
+                d2 = fmaf(ST[j + 2], gs.a[p][j + 2], d2);
+                d3 = fmaf(ST[j + 3], gs.a[p][j + 3], d3);
+            }
+            dr = (d0 + d1) + (d2 + d3);
+        }
 
-        const float idi = 1.f / di;
+        const float idi = __fdividef(1.f, di);
         float dw = 0.f, dk = 0.f, dv = 0.f, db = 0.f, dSb = 0.f;
 #pragma unroll
         for (int j = 0; j < NMAX; ++j) {
@@ -174,13 +194,36 @@ __global__ void __launch_bounds__(NMAX) wkv7_backward_kernel(
         }
         dsb[i] = dSb;
         __syncthreads();
-        float da = 0.f;
+        if (t >= kAhead && live) {   // the rows of a later token into L1: the loads below then find them there
+            const i64 o = base + (i64)(t - kAhead) * C;
+            if (line_lead) {
+                prefetch_l1(r_ + o); prefetch_l1(w_ + o); prefetch_l1(k_ + o); prefetch_l1(v_ + o);
+                prefetch_l1(a_ + o); prefetch_l1(b_ + o); prefetch_l1(dy_ + o);
+            }
+            if (line_lead_sa) prefetch_l1(sa_ + o);
+        }
+        if (t > 0 && live) {   // the next token, requested here: the registers it takes are not live in the loop above
+            const i64 o = base + (i64)(t - 1) * C;
+            rn = to_f(r_[o]); wn = to_f(w_[o]); kn = to_f(k_[o]); vn = to_f(v_[o]);
+            an = to_f(a_[o]); bn = to_f(b_[o]); gn = to_f(dy_[o]); sn = sa_[o];
+        }
+        float da;
+        {
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < NMAX; ++j) {
-            const float x = dsb[j];
-            da = fmaf(ST[j], x, da);
-            DR[j] = fmaf(DR[j], ds.a[p][j], dSb * as.a[p][j]);
-            DT[j] = fmaf(DT[j], di, ai * x);
+            for (int j = 0; j < NMAX; j += 4) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float x = dsb[j + q];
+                    if (q == 0) a0 = fmaf(ST[j + q], x, a0);
+                    if (q == 1) a1 = fmaf(ST[j + q], x, a1);
+                    if (q == 2) a2 = fmaf(ST[j + q], x, a2);
+                    if (q == 3) a3 = fmaf(ST[j + q], x, a3);
+                    DR[j + q] = fmaf(DR[j + q], ds.a[p][j + q], dSb * as.a[p][j + q]);
+                    DT[j + q] = fmaf(DT[j + q], di, ai * x);
+                }
+            }
+            da = (a0 + a1) + (a2 + a3);
         }
         if (live) {
             const i64 o = base + (i64)t * C;
