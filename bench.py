@@ -270,9 +270,9 @@ def _cpu_time(fn, repeat=2):
     return (time.perf_counter() - t0) / repeat
 
 
-def run_secondary(op, args):
-    """BASELINE configurations 1-4.  Prints one JSON line: tokens/s (or rows/s), per-kernel times, the
-    roofline of the backward kernel and the CPU formula path on a bounded sample."""
+def run_secondary(op, args, emit=True):
+    """BASELINE configurations 1-4.  Prints one JSON line (or returns it as a dict when `emit` is false): tokens/s
+    (or rows/s), per-kernel times, the roofline of the backward kernel and the CPU formula path on a bounded sample."""
     import rwkv_cuda_b200 as R
     from oracle import wkv_oracle as O
     dev = torch.device("cuda", 0)
@@ -337,7 +337,7 @@ def run_secondary(op, args):
         def bwd():
             R.ops.wkv5_backward_saved(B, T, C, H, r, k, v, eew, ew, u, gy, gr, gk, gv, gw, gu, saved5, valid5[0])
         bytes_f, bytes_b = 8 * C * B * T, 14 * C * B * T
-        bound, note = "hbm", "chunked tensor-core kernels (mma.sync TF32), decay constant over time"
+        bound, note = "hbm", "tcgen05 kernels on 32-token chunks, chunk states saved by the forward; decay constant over time"
         Tc = 256
 
         def cpu():
@@ -366,7 +366,7 @@ def run_secondary(op, args):
             R.ops.wkv6state_backward_saved(B, T, C, H, r, k, v, wraw, u, s0, gy, dsT, gr, gk, gv, gw, gu, ds0, saved, valid[0])
         st = 4 * B * H * N * N
         bytes_f, bytes_b = 10 * C * B * T + 2 * st, 18 * C * B * T + 2 * st
-        bound, note = "hbm", "chunked tensor-core kernels (mma.sync TF32), per-token decay, fp32 state in/out"
+        bound, note = "hbm", "tcgen05 kernels on 32-token chunks, chunk states saved by the forward; per-token decay, fp32 state in/out"
         Tc = 256
 
         def cpu():
@@ -393,12 +393,15 @@ def run_secondary(op, args):
     out = {"metric": f"{op} fwd+bwd tokens/s", "value": tokens / ((fwd_ms + bwd_ms) * 1e-3), "unit": "tokens/s", "n_gpus": 1,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": fwd_ms + bwd_ms, "higher_is_better": True,
            "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": name},
-           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, # wkv6state, wkv5: chunked forward + its guarded general-shape twin, then forward rebuild, chunked backward and twin
-           "gpu_launches": (5 if op in ("wkv6state", "wkv5") else 3 if op == "timex" else 2) * args.steps,
+           "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof,
+           # wkv6state, wkv5: tensor-core forward and backward, each followed by its guarded general-shape twin
+           "gpu_launches": (4 if op in ("wkv6state", "wkv5") else 3 if op == "timex" else 2) * args.steps,
            "clocks": clocks.summary()}
     if not args.no_cpu_baseline:
         ct = _cpu_time(cpu)
         out["cpu_baseline"] = {"value": cpu_tokens / ct, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": cpu_sample}
+    if not emit:
+        return out
     print(json.dumps(out), flush=True)
 
 
@@ -519,6 +522,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the short runs of BASELINE configurations 1-4 after the main one")
     ap.add_argument("--cpu-seq", type=int, default=256, help="sequence length of one CPU-baseline step (B=1, C=4096)")
     ap.add_argument("--batch", type=int, default=None, help="profiling aid: smaller global batch than the config's 16")
     ap.add_argument("--seq", type=int, default=None, help="profiling aid: shorter sequence than the config's 4096")
@@ -655,6 +659,21 @@ def main():
             "clocks": clocks.summary(),
             "reference_kernel": ref_kernel_block,
         }
+        if world == 1 and not args.no_other_configs and not (args.batch or args.seq or args.path):
+            # the other BASELINE configurations, a few steps each, so that one record covers them all
+            import copy
+            a2 = copy.copy(args)
+            a2.steps, a2.warmup, a2.no_cpu_baseline, a2.batch, a2.seq = 5, 3, True, None, None
+            del wl
+            torch.cuda.empty_cache()
+            other = {}
+            for op in ("wkv4", "timex", "wkv5", "wkv6state"):
+                o = run_secondary(op, a2, emit=False)
+                other[op] = {"workload": o["config"]["workload"], "fwd_ms": o["fwd_ms"], "bwd_ms": o["bwd_ms"],
+                             "tokens_per_s": o["value"], "dtype": o["dtype"],
+                             "roofline": {k: o["roofline"][k] for k in ("bound", "achieved", "peak", "unit", "frac")},
+                             "roofline_fwd_frac": o["roofline"]["fwd"]["frac"]}
+            out["other_configs"] = other
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             T_cpu = args.cpu_seq
