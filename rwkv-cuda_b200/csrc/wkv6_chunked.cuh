@@ -31,6 +31,8 @@ int wkv6_l32_backward(int B, int T, int H, const void* r, const void* k, const v
                       const void* gy, const float* dsT, const float* ck, void* gr, void* gk, void* gv, void* gw, void* gu,
                       void* ds0, int ds0_kind, cudaStream_t st, float* gw32 = nullptr, float* gu32 = nullptr);
 int wkv6_l32_bwd_error(int clear);
+// a tensor map over a (rows, cols) bf16 or fp32 tensor, box [32 rows][64 columns], no swizzle; false if it cannot be made
+bool wkv6_make_tile_map(void* map, const void* base, unsigned long long rows, unsigned long long cols, bool fp32);
 int wkv6_l32_error(int clear);   // sticky status word of that kernel: read (clear = 0) or reset (clear = 1)
 // 0 = the mma.sync kernel of wkv6_chunked.cu for every forward, 1 (default) = the tcgen05 kernel where it applies
 void wkv6_select_forward(int tcgen05);

@@ -46,8 +46,10 @@ struct Smem {
     static constexpr int kA0 = kWe + 256;                // [2][64]
     static constexpr int kCarry = kA0 + 512;             // [64]
     static constexpr int kGam = kCarry + 256;            // [32]
-    static constexpr int kBar = kGam + 128;              // mbarriers + tmem slot
-    static constexpr int kBytes = kBar + 64 + 1024;
+    static constexpr int kBar = kGam + 128;              // 7 mbarriers + tmem slot
+    static constexpr int kRaw = kBar + 128;              // the next chunk's inputs as the copy engine delivers them:
+                                                         // r, k, v, gy [32][64] bf16 each, then the decay input (bf16 or fp32)
+    static constexpr int kBytes = kRaw + 4 * 4096 + 8192 + 1024;
     static constexpr int kHs = kAm;                      // [8][64] exchange buffer of the preparation (A, G not yet written)
 };
 static_assert(Smem::kBytes <= 115712 && 8 * 64 * 4 <= 2 * HALF32, "two CTAs per SM");
@@ -82,7 +84,8 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     float* Gam = reinterpret_cast<float*>(smem + Smem::kGam);
     float* Hs = reinterpret_cast<float*>(smem + Smem::kHs);
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + Smem::kBar);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 6);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 7);
+    unsigned char* Raw = smem + Smem::kRaw;
 
     const int hh = blockIdx.x, bb = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -99,7 +102,7 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 6; ++i) mbar_init(bar + i);
+        for (int i = 0; i < 7; ++i) mbar_init(bar + i);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -143,35 +146,69 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     }
 
     RawChunk<4, BTPW> raw;
-    float wl0[BTPW], wl1[BTPW];   // log2 decay of this thread's tokens (two channels)
+    // the decay input of this thread's tokens (two channels) as loaded: decoded where it is used, one chunk later, so
+    // that nothing waits for the load where it is issued
+    uint32_t wraw[BTPW];      // WMODE 1: two bf16
+    float2 wlog[BTPW];        // WMODE 0: two fp32 log-decays
+    bool win[BTPW];
     auto fetch = [&](int c) {
         fetch_chunk<4, BTPW>(raw, src, tok0, C, c, T, warp, lane);
         const int t0 = c * LC + BTPW * warp;
 #pragma unroll
         for (int q = 0; q < BTPW; ++q) {
             const bool in = t0 + q < T;
+            win[q] = in;
             if (WMODE == 1) {
-                const uint32_t x = in ? __ldg(reinterpret_cast<const unsigned int*>(reinterpret_cast<const bf16*>(w_) + tok0 + (i64)(t0 + q) * C + j0)) : 0u;
-                const float2 w2 = bf16x2_to_f2(x);
-                wl0[q] = in ? -fexp(w2.x) * 1.4426950408889634f : 0.f;
-                wl1[q] = in ? -fexp(w2.y) * 1.4426950408889634f : 0.f;
+                wraw[q] = in ? __ldg(reinterpret_cast<const unsigned int*>(reinterpret_cast<const bf16*>(w_) + tok0 + (i64)(t0 + q) * C + j0)) : 0u;
             } else if (WMODE == 0) {
-                float2 w2 = make_float2(0.f, 0.f);
-                if (in) w2 = __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(w_) + tok0 + (i64)(t0 + q) * C + j0));
-                wl0[q] = w2.x * 1.4426950408889634f;
-                wl1[q] = w2.y * 1.4426950408889634f;
-            } else {
-                wl0[q] = in ? ls0 : 0.f;
-                wl1[q] = in ? ls1 : 0.f;
+                wlog[q] = make_float2(0.f, 0.f);
+                if (in) wlog[q] = __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(w_) + tok0 + (i64)(t0 + q) * C + j0));
             }
         }
     };
-    fetch(nchunks - 1);
-    // two chunks ahead, into L2: the tiles of r, k, v, gy (and of a bf16 per-token decay) and the chunk-start state
-    auto ask_l2 = [&](int c) {
-        if (tid != 224 || !maps.valid) return;
+    // The same through the copy engine, when tensor maps could be made: one thread asks for the tiles of chunk c
+    // (counted in bytes on mbarrier 6), and at the top of that chunk every thread takes its words out of the staged tiles.
+    constexpr int kRawBytes = 4 * 4096 + (WMODE == 1 ? 4096 : WMODE == 0 ? 8192 : 0);
+    auto request = [&](int c) {
+        mbar_expect_bytes(bar + 6, kRawBytes);
 #pragma unroll
-        for (int q = 0; q < (WMODE == 1 ? 5 : 4); ++q) l2_prefetch_tile(&maps.m[q], hh * 64, bb * T + c * LC);
+        for (int x = 0; x < 4; ++x) tma_tile_load(Raw + x * 4096, &maps.m[x], hh * 64, bb * T + c * LC, bar + 6);
+        if (WMODE <= 1) tma_tile_load(Raw + 4 * 4096, &maps.m[4], hh * 64, bb * T + c * LC, bar + 6);
+    };
+    auto take = [&](int c) {
+        const int t0 = c * LC + BTPW * warp;
+#pragma unroll
+        for (int q = 0; q < BTPW; ++q) {
+            const bool in = t0 + q < T;
+            const int row = BTPW * warp + q;
+            win[q] = in;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) raw.x[x][q] = in ? *reinterpret_cast<const uint32_t*>(Raw + x * 4096 + row * 128 + lane * 4) : 0u;
+            if (WMODE == 1) wraw[q] = in ? *reinterpret_cast<const uint32_t*>(Raw + 4 * 4096 + row * 128 + lane * 4) : 0u;
+            if (WMODE == 0) wlog[q] = in ? *reinterpret_cast<const float2*>(Raw + 4 * 4096 + row * 256 + lane * 8) : make_float2(0.f, 0.f);
+        }
+    };
+    const bool staged = maps.valid != 0;
+    bool pending = false;   // a request whose tiles have not been taken yet
+    // log2 decay of token q of the fetched chunk, channels j0 and j0 + 1
+    auto decay_log2 = [&](int q, float& l0, float& l1) {
+        if (WMODE == 1) {
+            const float2 w2 = bf16x2_to_f2(wraw[q]);
+            l0 = win[q] ? -fexp(w2.x) * 1.4426950408889634f : 0.f;
+            l1 = win[q] ? -fexp(w2.y) * 1.4426950408889634f : 0.f;
+        } else if (WMODE == 0) {
+            l0 = wlog[q].x * 1.4426950408889634f;
+            l1 = wlog[q].y * 1.4426950408889634f;
+        } else {
+            l0 = win[q] ? ls0 : 0.f;
+            l1 = win[q] ? ls1 : 0.f;
+        }
+    };
+    if (!staged) fetch(nchunks - 1);
+    else { if (tid == 0) request(nchunks - 1); pending = true; }
+    // two chunks ahead, into L2: the chunk-start state (the input tiles come by the copy engine one chunk ahead)
+    auto ask_l2 = [&](int c) {
+        if (tid != 224) return;
         const float* sp = ck + (i64)c * 64 * 64;
         if ((reinterpret_cast<uintptr_t>(sp) & 15) == 0) l2_prefetch(sp, 64 * 64 * 4);
     };
@@ -195,12 +232,22 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             cp_async_commit();
         }
         // ---- 1. operands: this thread has channels j0, j0+1 of tokens 4*warp .. 4*warp+3 ----------------
+        if (staged) {
+            if (!mbar_wait(bar + 6, par)) fail = 6;
+            take(c);
+            pending = false;
+        }
         {
             float cs0[BTPW], cs1[BTPW], run0 = 0.f, run1 = 0.f;
 #pragma unroll
-            for (int q = 0; q < BTPW; ++q) { run0 += wl0[q]; run1 += wl1[q]; cs0[q] = run0; cs1[q] = run1; }
+            for (int q = 0; q < BTPW; ++q) {
+                float l0, l1;
+                decay_log2(q, l0, l1);
+                run0 += l0; run1 += l1; cs0[q] = run0; cs1[q] = run1;
+            }
             *reinterpret_cast<float2*>(Hs + warp * 64 + j0) = make_float2(run0, run1);
             __syncthreads();
+            if (staged && c > 0) { if (tid == 0) request(c - 1); pending = true; }   // every thread has taken its words: the stage is free
             float base0 = 0.f, base1 = 0.f, tot0 = 0.f, tot1 = 0.f;
 #pragma unroll
             for (int gq = 0; gq < 8; ++gq) {
@@ -258,7 +305,7 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tmem_st_tiles<4>(tmET + 32 * hs + lane_off, Td);
             tmem_wait_st();
         }
-        if (c > 0) fetch(c - 1);
+        if (c > 0 && !staged) fetch(c - 1);
         if (c > 1) ask_l2(c - 2);
         if (!mbar_wait(bar, par)) fail = 1;
         tc_fence_after();
@@ -439,6 +486,7 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
     }
 
+    if (pending) mbar_wait(bar + 6, par);   // leaving early: the requested tiles must have landed before the block may end
     if (fail && tid == 0) {   // a wait ran out: record it and poison this unit's outputs
         atomicMax(&g_v6b_error, fail);
         gr_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
@@ -498,8 +546,10 @@ int wkv6_l32_backward(int B, int T, int H, const void* r, const void* k, const v
                       void* ds0, int ds0_kind, cudaStream_t st, float* gw32, float* gu32) {
     using namespace v6b;
     TileMaps<5> maps;
-    const void* in[5] = {r, k, v, gy, w_mode == 1 ? w : r};
-    make_tile_maps<5>(maps, in, B, T, H);
+    const void* in[5] = {r, k, v, gy, w_mode <= 1 ? w : r};
+    maps.valid = 1;
+    for (int x = 0; x < 5 && maps.valid; ++x)
+        if (!wkv6_make_tile_map(&maps.m[x], in[x], (unsigned long long)B * T, (unsigned long long)H * 64, x == 4 && w_mode == 0)) maps.valid = 0;
     dim3 grid(H, B);
 #define RWKV_GO(M)                                                                                                        \
     do {                                                                                                                  \

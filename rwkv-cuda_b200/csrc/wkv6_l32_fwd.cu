@@ -433,6 +433,10 @@ bool make_map6(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, b
 }
 }  // namespace
 
+bool wkv6_make_tile_map(void* map, const void* base, unsigned long long rows, unsigned long long cols, bool fp32) {
+    return encode_tiled6() != nullptr && make_map6(reinterpret_cast<CUtensorMap*>(map), base, rows, cols, fp32);
+}
+
 // Returns RWKVB200_OK, an error code, or 1 when tensor maps cannot be made here (the caller then uses the
 // mma.sync kernel of wkv6_chunked.cu).  Arguments as wkv6_chunked_forward; ck (optional): the states at the start of
 // every 32-token chunk, (B,H,ceil(T/32),N,N) fp32, for wkv6_l32_backward; y may then be NULL (states only).

@@ -187,6 +187,17 @@ struct TileMaps {
     CUtensorMap m[NX];
     int valid;   // 0: no maps could be made, nothing is requested
 };
+// One [32 rows][64 columns] tile of a tensor map (x = first column, y = first row) -> shared memory as plain rows, by
+// the copy engine; completion is counted in bytes on the mbarrier, on which one thread has announced them before.
+__device__ __forceinline__ void tma_tile_load(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_expect_bytes(uint64_t* bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void l2_prefetch_tile(const CUtensorMap* map, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
                  : "memory");
