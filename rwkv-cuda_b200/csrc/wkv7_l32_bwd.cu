@@ -47,8 +47,11 @@ struct BwdSmemX {
     static constexpr int kWe = kLam + 32 * LAMP * 4;     // [64]
     static constexpr int kA0 = kWe + 256;                // [2][64] partial anchors
     static constexpr int kCarry = kA0 + 512;             // [64] sum of c over the first 16 tokens
-    static constexpr int kBar = kCarry + 256;            // 7 mbarriers + tmem slot
-    static constexpr int kBytes = kBar + 64 + 1024;      // + slack to start on a 1024-byte boundary
+    static constexpr int kBar = kCarry + 256;            // 8 mbarriers + tmem slot
+    static constexpr int kBytes = kBar + 128 + 1024;     // + slack to start on a 1024-byte boundary
+    // the next chunk's seven input tiles ([32 tokens][64 channels] bf16, 4 KB each) as the copy engine delivers
+    // them: in EY and the first 12 KB of S0, which are dead from the last products of a chunk to the preparation of the next
+    static constexpr int kRaw = kEY;
     // inside the EV rows of EY (two pieces of 4096 bytes), free until EV is written: the exchange buffer
     // and the two diagonal blocks of U_ab, plain fp32 [2][16][BPITCH]
     static constexpr int kHs = kEY;                      // [8][64]
@@ -106,7 +109,8 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     float* Hs = reinterpret_cast<float*>(smem + BwdSmemX::kHs);
     float* Uab = reinterpret_cast<float*>(smem + BwdSmemX::kUab);
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + BwdSmemX::kBar);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 7);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 8);
+    unsigned char* Raw = smem + BwdSmemX::kRaw;
 
     const int hh = blockIdx.x, bb = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -122,7 +126,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 7; ++i) mbar_init(bar + i);
+        for (int i = 0; i < 8; ++i) mbar_init(bar + i);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -166,7 +170,26 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     };
 
     RawChunk<7, BTPW> raw;
-    fetch_chunk<7, BTPW>(raw, src, tok0, C, nchunks - 1, T, warp, lane);
+    // With tensor maps the inputs come by the copy engine: one thread asks for the seven tiles of a chunk (counted in
+    // bytes on mbarrier 7) when the arrays that receive them are dead, and at the top of that chunk every thread takes
+    // its words out of them; without maps every thread loads its words itself, one chunk ahead, into registers.
+    const bool staged = maps.valid != 0;
+    bool pending = false;   // a request whose tiles have not been taken yet
+    auto request = [&](int c) {
+        mbar_expect_bytes(bar + 7, 7 * 4096);
+#pragma unroll
+        for (int x = 0; x < 7; ++x) tma_tile_load(Raw + x * 4096, &maps.m[x], hh * 64, bb * T + c * LC, bar + 7);
+    };
+    auto take = [&](int c) {
+        const int t0 = c * LC + BTPW * warp;
+#pragma unroll
+        for (int x = 0; x < 7; ++x)
+#pragma unroll
+            for (int q = 0; q < BTPW; ++q)
+                raw.x[x][q] = (t0 + q < T) ? *reinterpret_cast<const uint32_t*>(Raw + x * 4096 + (BTPW * warp + q) * 128 + lane * 4) : 0u;
+    };
+    if (staged) { if (tid == 0) request(nchunks - 1); pending = true; }
+    else fetch_chunk<7, BTPW>(raw, src, tok0, C, nchunks - 1, T, warp, lane);
     if (nchunks > 1 && tid == 224) prefetch_chunk_l2<7>(maps, hh * 64, bb * T + (nchunks - 2) * LC, ck + (i64)(nchunks - 2) * 64 * 64, 64 * 64 * 4);
     int fail = 0;
     uint32_t par = 0;
@@ -179,6 +202,12 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         if (__syncthreads_or(fail)) break;
         tc_fence_after();
         WKV7_PHASE(0);   // top barrier
+        if (staged) {
+            if (!mbar_wait(bar + 7, par)) fail = 9;
+            take(c);
+            pending = false;
+            __syncthreads();   // the tiles lie where the state and the scratch of the preparation go next
+        }
         fetch_state(c);
         // the zero blocks of D0 (its space was used by P)
         {
@@ -247,7 +276,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tmem_st_tiles<4>(tmET + 32 * hs + lane_off, Td);
             tmem_wait_st();
         }
-        if (c > 0) fetch_chunk<7, BTPW>(raw, src, tok0, C, c - 1, T, warp, lane);   // under the chain
+        if (c > 0 && !staged) fetch_chunk<7, BTPW>(raw, src, tok0, C, c - 1, T, warp, lane);   // under the chain
         if (c > 1 && tid == 224) prefetch_chunk_l2<7>(maps, hh * 64, bb * T + (c - 2) * LC, ck + (i64)(c - 2) * 64 * 64, 64 * 64 * 4);   // the one after into L2
         WKV7_PHASE(5);   // issue of the forward part, decay scaling of E, request of the next chunk
         if (!mbar_wait(bar + 1, par)) fail = 2;
@@ -450,6 +479,8 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             if (hs == 0 && t == 0) { Carry[row0 + g] = run[0]; Carry[row0 + g + 8] = run[1]; }
         }
         __syncthreads();
+        // every product that reads EY or S0 has completed and every thread has taken its anchor from S0
+        if (staged && c > 0) { if (tid == 0) request(c - 1); pending = true; }
         WKV7_PHASE(13);  // epilogue part 1
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -482,6 +513,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         WKV7_PHASE(14);  // dw out
     }
 
+    if (pending) mbar_wait(bar + 7, par);   // leaving early: the requested tiles must have landed before the block may end
     if (fail && tid == 0) {   // a wait ran out: record it and poison this unit's outputs so that they cannot pass as results
         atomicMax(&g_l32_bwd_error, fail);
         dr_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
