@@ -63,8 +63,8 @@ struct PipeSmem {
     static constexpr int kSet1 = SetSmem::kBytes;
     static constexpr int kA0 = 2 * SetSmem::kBytes;      // [2][64]
     static constexpr int kCarry = kA0 + 512;             // [64]
-    static constexpr int kBar = kCarry + 256;            // 14 mbarriers, tmem slot, abort word
-    static constexpr int kBytes = kBar + 128 + 1024;
+    static constexpr int kBar = kCarry + 256;            // 15 mbarriers, tmem slot, abort words, request counters
+    static constexpr int kBytes = kBar + 256 + 1024;
 };
 static_assert(PipeSmem::kBytes <= 232448, "fits the shared memory of one SM");
 
@@ -115,8 +115,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 // mbarriers: 0-1 full[set], 2-3 empty[set] (one arrival each); front: 4 U, 5-6 SA[set], 7 its chain; back: 8 EV,
-// 9 P, 10 E/ET, 11 gradients, 12 its chain
-enum { kFull = 0, kEmpty = 2, kFU = 4, kFSA = 5, kFChain = 7, kBEV = 8, kBP = 9, kBE = 10, kBG = 11, kBChain = 12, kNBar = 13 };
+// 9 P, 10 E/ET, 11 gradients, 12 its chain; 13-14 the staged input tiles of a set have landed
+enum { kFull = 0, kEmpty = 2, kFU = 4, kFSA = 5, kFChain = 7, kBEV = 8, kBP = 9, kBE = 10, kBG = 11, kBChain = 12, kRaw = 13, kNBar = 15 };
 
 __global__ void __launch_bounds__(PNT, 1)
 wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __restrict__ w_,
@@ -124,7 +124,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                       const bf16* __restrict__ b_, const bf16* __restrict__ dy_, const float* __restrict__ dsT_,
                       const float* __restrict__ ck_, float* __restrict__ ds0_, bf16* __restrict__ dr_,
                       bf16* __restrict__ dw_, bf16* __restrict__ dk_, bf16* __restrict__ dv_, bf16* __restrict__ da_,
-                      bf16* __restrict__ db_) {
+                      bf16* __restrict__ db_, const __grid_constant__ TileMaps<7> maps) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     float* A0p = reinterpret_cast<float*>(smem + PipeSmem::kA0);
@@ -133,6 +133,8 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + kNBar);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* gabort = abort_word + 1;   // [2]: each group's copy, so that all its threads take the same decision
+    volatile int* raw_req = gabort + 2;      // [2]: tile requests issued per set;  raw_got = raw_req + 2: [2] requests whose tiles were taken
+    volatile int* raw_got = raw_req + 2;
 
     const int hh = blockIdx.x, bb = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -151,6 +153,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
 #pragma unroll
         for (int i = 0; i < kNBar; ++i) mbar_init(bar + i);
         *abort_word = 0; gabort[0] = 0; gabort[1] = 0;
+        raw_req[0] = raw_req[1] = raw_got[0] = raw_got[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -174,10 +177,27 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     long long pipe_last_ = clock64();
 #endif
 
+    // With tensor maps the inputs of a chunk come by the copy engine into EY and the first 12 KB of S0 of the set that
+    // the chunk will use, as soon as the chunk that used the set before has no more use for them: asked for by one
+    // thread of the back group after its last products (by the front group for the first two chunks), counted in
+    // bytes on the set's mbarrier; the front group takes its words out of the tiles before it writes the set.
+    const bool staged = maps.valid != 0;
+    auto request = [&](int set, int c) {
+        unsigned char* dst = smem + set * PipeSmem::kSet1 + SetSmem::kEY;
+        mbar_expect_bytes(bar + kRaw + set, 7 * 4096);
+#pragma unroll
+        for (int x = 0; x < 7; ++x) tma_tile_load(dst + x * 4096, &maps.m[x], hh * 64, bb * T + c * LC, bar + kRaw + set);
+        raw_req[set] = raw_req[set] + 1;
+    };
+
     // ================================ front group ==========================================================
     if (grp == 0) {
         RawChunk<7, 4> raw;
-        fetch_chunk<7, 4>(raw, src, tok0, C, nchunks - 1, T, wg, lane);
+        if (!staged) fetch_chunk<7, 4>(raw, src, tok0, C, nchunks - 1, T, wg, lane);
+        else if (gtid == 0) {
+            request(0, nchunks - 1);
+            if (nchunks > 1) request(1, nchunks - 2);
+        }
         ChainSync cs{bar + kFChain, 0, 0};   // used by the group's warp 0 only
         // dr, da, dk, db, dw of chunk cp, staged as bf16 rows by the back group in dead arrays of the set at
         // `sbase_`, go to global memory from this group (thread = token, 16-byte piece), which has the time.
@@ -217,10 +237,18 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             if (gtid == 0) gabort[0] = *abort_word;
             group_sync(gbar, GNT);
             if (gabort[0]) break;
-            if (it >= 2) {   // the set holds the staged outputs of the chunk that used it last: they leave from here
-                flush_outputs(base, c + 2);
-                group_sync(gbar, GNT);
+            if (it >= 2) flush_outputs(base, c + 2);   // the set holds the staged outputs of the chunk that used it last: they leave from here
+            if (staged) {
+                if (!mbar_wait(bar + kRaw + set, (it >> 1) & 1)) fail = 36;
+                const unsigned char* rawt = base + SetSmem::kEY;
+#pragma unroll
+                for (int x = 0; x < 7; ++x)
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        raw.x[x][q] = (c * LC + 4 * wg + q < T) ? *reinterpret_cast<const uint32_t*>(rawt + x * 4096 + (4 * wg + q) * 128 + lane * 4) : 0u;
+                if (gtid == 0) raw_got[set] = raw_got[set] + 1;
             }
+            if (it >= 2 || staged) group_sync(gbar, GNT);   // before the set is written
             {   // chunk-start state -> S0 (swizzled), 16-byte pieces
                 const float* s0g = ck + (i64)c * 64 * 64;
 #pragma unroll
@@ -248,7 +276,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int ks = 0; ks < 8; ++ks)   // X_a = S0 A~^T, needed after the inverse only
                     mma_ss(tmF2, desc_k(s0A, 0, ks * 8, HALF64), desc_k(arA, 0, ks * 8, HALF64), idesc64(32, 0, 0), ks > 0, lead);
             }
-            if (c > 0) fetch_part<0, 4>(raw, src, tok0, C, c - 1, T, wg, lane);   // the next chunk, first part: under U
+            if (c > 0 && !staged) fetch_part<0, 4>(raw, src, tok0, C, c - 1, T, wg, lane);   // the next chunk, first part: under U
             PIPE_MARK(2);
             if (!mbar_wait(bar + kFU, par)) fail = 31;
             PIPE_MARK(3);
@@ -273,11 +301,11 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     mma_ss(tmF2, desc_mn(svA + 32 * 128, ks * 8, HALF64), desc_mn(uakA, ks * 8, HALF32), idesc64(32, 1, 1), 1, lead);
                 cs.sync(lead);
                 issue_solve(tmF2 + 32, tmF2, d0A, n1A, lead, cs, [&]() {   // SA = Z T
-                    if (c > 0) fetch_part<4, 7>(raw, src, tok0, C, c - 1, T, wg, lane);
+                    if (c > 0 && !staged) fetch_part<4, 7>(raw, src, tok0, C, c - 1, T, wg, lane);
                 });
                 mma_commit(bar + kFSA + set, lead);   // the back group takes SA out of tensor memory
                 if (cs.fail) fail = 32;
-            } else if (c > 0) {
+            } else if (c > 0 && !staged) {
                 fetch_part<4, 7>(raw, src, tok0, C, c - 1, T, wg, lane);   // the next chunk, second part: under the chain
             }
             PIPE_MARK(5);
@@ -552,6 +580,9 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
             tc_fence_before();
             group_sync(gbar, GNT);
+            // every product that reads EY or S0 of this set has completed and every thread has taken its anchor from S0:
+            // the tiles of the chunk that uses the set next may come
+            if (staged && c >= 2 && gtid == 0) request(set, c - 2);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int j = row0 + g + 8 * h;
@@ -575,6 +606,10 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     __syncthreads();
     tc_fence_after();
     const int ab = *abort_word;
+    if (ab && tid == 0) {   // leaving early: tiles that were asked for and not taken must have landed before the block may end
+        for (int set = 0; set < 2; ++set)
+            for (int k = raw_got[set]; k < raw_req[set]; ++k) mbar_wait(bar + kRaw + set, k & 1);
+    }
     if (ab && tid == 0) {   // a wait ran out: record it and poison this unit's outputs so that they cannot pass as results
         atomicMax(&g_l32_bwdp_error, ab);
         dr_[tok0] = __ushort_as_bfloat16((unsigned short)0x7fc0);
@@ -604,11 +639,14 @@ int wkv7_l32_backward_pipelined(int B, int T, int H, const void* r, const void* 
     using namespace v7p;
     cudaError_t e = cudaFuncSetAttribute(wkv7p_backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PipeSmem::kBytes);
     RWKV_REQUIRE(e == cudaSuccess, RWKVB200_ECUDA, "wkv7_backward: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    TileMaps<7> maps;
+    const void* in[7] = {r, w, k, v, a, b, dy};
+    make_tile_maps<7>(maps, in, B, T, H);
     dim3 grid(H, B);
     wkv7p_backward_kernel<<<grid, PNT, PipeSmem::kBytes, st>>>(T, H, (const bf16*)r, (const bf16*)w, (const bf16*)k,
                                                                (const bf16*)v, (const bf16*)a, (const bf16*)b, (const bf16*)dy,
                                                                dsT, s, ds0, (bf16*)dr, (bf16*)dw, (bf16*)dk, (bf16*)dv,
-                                                               (bf16*)da, (bf16*)db);
+                                                               (bf16*)da, (bf16*)db, maps);
     return check_launch("wkv7_backward(tcgen05, 32-token chunks, two stages)");
 }
 
