@@ -298,6 +298,10 @@ int rwkvb200_device_status_clear(void);
  * tensor memory, orderly return) can be exercised with nothing in flight.  That call's outputs are
  * invalid.  No counterpart in the reference. */
 int rwkvb200_wkv7_test_expire_next_forward(void);
+/* Test hook: on != 0 makes the library behave as if the driver could not make tensor maps, so that the kernels that
+ * load their inputs without TMA (the one-group RWKV-7 forward, the plain-load paths of the backward kernels, the
+ * mma.sync RWKV-5/6 forward) run; 0 restores the normal choice.  Process-wide.  No counterpart in the reference. */
+int rwkvb200_test_disable_tensor_maps(int on);
 
 #ifdef __cplusplus
 }

@@ -76,6 +76,13 @@ extern "C" int rwkvb200_wkv7_select_path(int path) {
     return RWKVB200_OK;
 }
 
+static std::atomic<int> g_no_tensor_maps{0};
+bool rwkvb200::tensor_maps_disabled() { return g_no_tensor_maps.load() != 0; }
+extern "C" int rwkvb200_test_disable_tensor_maps(int on) {
+    g_no_tensor_maps.store(on ? 1 : 0);
+    return RWKVB200_OK;
+}
+
 extern "C" int rwkvb200_wkv7_test_expire_next_forward(void) {
     g_wkv7_test_expire.store(1);
     return RWKVB200_OK;

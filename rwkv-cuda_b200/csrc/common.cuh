@@ -53,6 +53,10 @@ int check_launch(const char* what);
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// test hook (rwkvb200_test_disable_tensor_maps): true makes every tensor-map maker report failure, so that the
+// paths that load without TMA run on a machine that has it
+bool tensor_maps_disabled();
+
 // smallest instantiated head-size capacity holding N (32, 64 or 128), or 0
 inline int head_capacity(int N) { return N <= 0 ? 0 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 0; }
 

@@ -304,3 +304,40 @@ def test_rwkv5_saved_states_flow(R, B, T, H, hi):
         assert torch.isfinite(x.float()).all(), name
         Hh.assert_close(x, want, Hh.TOL_BF16, f"{name} (RWKV-5 saved-states flow)")
     Hh.assert_close(gw.float().sum(0), xs[3].grad, Hh.TOL_BF16, "gw from the bf16 partials")
+
+
+@pytest.mark.parametrize("B,T,H", [(2, 256, 3), (1, 48, 2)])
+def test_rwkv6_backward_without_tensor_maps(R, B, T, H):
+    """The tcgen05 RWKV-6 backward when it cannot make tensor maps (test hook): it loads its inputs with plain loads
+    instead of TMA and the gradients are bit-identical.  The states come from a forward that ran with maps."""
+    from rwkv_cuda_b200 import _lib
+    N = 64
+    C = H * N
+    r, k, v, w_raw, u, s0 = _v6_inputs(B, T, H, N, seed=51)
+    g = Hh.gen(52)
+    gy, dsT = Hh.randn(g, B, T, C), Hh.randn(g, B, H, N, N)
+    rd, kd, vd, wd, ud, gd = (x.to(BF).to(DEV).contiguous() for x in (r, k, v, w_raw, u, gy))
+    s0d, dsTd = s0.to(DEV), dsT.to(DEV)
+    y, sT = torch.empty(B, T, C, dtype=BF, device=DEV), torch.empty(B, H, N, N, device=DEV)
+    saved = torch.empty(R.ops.wkv6_saved_bytes(B, T, C), dtype=torch.uint8, device=DEV)
+    valid = R.ops.wkv6state_forward_saved(B, T, C, H, rd, kd, vd, wd, ud, s0d, y, sT, saved)
+    assert valid
+
+    def run():
+        nan = float("nan")
+        gr, gk, gv, gw = (torch.full((B, T, C), nan, dtype=BF, device=DEV) for _ in range(4))
+        gu, ds0 = torch.full((B, C), nan, dtype=BF, device=DEV), torch.full((B, H, N, N), nan, device=DEV)
+        R.ops.wkv6state_backward_saved(B, T, C, H, rd, kd, vd, wd, ud, s0d, gd, dsTd, gr, gk, gv, gw, gu, ds0, saved, valid)
+        torch.cuda.synchronize()
+        return gr, gk, gv, gw, gu, ds0
+
+    a = run()
+    try:
+        _lib.call("rwkvb200_test_disable_tensor_maps", 1)
+        b = run()
+    finally:
+        _lib.call("rwkvb200_test_disable_tensor_maps", 0)
+    assert _lib.lib().rwkvb200_device_status() == 0
+    for x, y2, name in zip(a, b, ("gr", "gk", "gv", "gw", "gu", "ds0")):
+        assert torch.isfinite(x.float()).all(), name
+        assert torch.equal(x, y2), name

@@ -151,3 +151,30 @@ def test_bounded_wait_runs_out_and_the_library_recovers():
     for n in good:
         assert torch.equal(good[n], again[n]), n
     assert L.rwkvb200_device_status() == 0
+
+
+@pytest.mark.parametrize("form", [1, 2])
+@pytest.mark.parametrize("B,T,H", [(2, 64, 2), (1, 48, 2), (1, 512, 3)])
+def test_paths_without_tensor_maps_agree(form, B, T, H):
+    """With the test hook that makes every tensor map fail, the backward kernels load their inputs with plain loads
+    (and the forward falls back to its one-group form): the gradients are bit-identical to those of the TMA paths,
+    since only the way the same words reach the registers differs."""
+    import rwkv_cuda_b200 as R
+    from rwkv_cuda_b200 import _lib
+    inp = Hh.v7_inputs(B, T, H, 64, seed=23)
+    try:
+        _set_path(2)
+        _set_form(form)
+        with_maps = _run_both(R, inp, H, True, True)
+        _lib.call("rwkvb200_test_disable_tensor_maps", 1)
+        without = _run_both(R, inp, H, True, True)
+    finally:
+        _lib.call("rwkvb200_test_disable_tensor_maps", 0)
+        _set_form(0)
+        _set_path(0)
+    assert _lib.lib().rwkvb200_device_status() == 0
+    for n in ("dr", "dw", "dk", "dv", "da", "db", "ds0"):
+        assert torch.equal(with_maps[n], without[n]), n
+    # the forward differs in form (staged with maps, one group without when form != 1): equal up to rounding
+    for n in ("y", "sT"):
+        assert (with_maps[n].float() - without[n].float()).abs().max() <= 2e-2 * with_maps[n].float().abs().max(), n
