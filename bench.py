@@ -109,7 +109,7 @@ class V7Workload:
     # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernel per token, from the ncu
     # capture of the reduced case (profiles/wkv7_tcgen05_chunk32_B8_T1024.md); traffic is
     # proportional to the token count
-    dram_bytes_per_token_bwd = (0.749133e9 + 0.379207e9) / (8 * 1024)
+    dram_bytes_per_token_bwd = (0.758777e9 + 0.379956e9) / (8 * 1024)
 
     def e2e_step(self):
         """Host buffers in, host buffers out, through the public host-buffer API
