@@ -154,7 +154,7 @@ def test_bounded_wait_runs_out_and_the_library_recovers():
 
 
 @pytest.mark.parametrize("form", [1, 2])
-@pytest.mark.parametrize("B,T,H", [(2, 64, 2), (1, 48, 2), (1, 512, 3)])
+@pytest.mark.parametrize("B,T,H", [(2, 64, 2), (1, 48, 2), (1, 512, 3), (1, 16400, 2)])
 def test_paths_without_tensor_maps_agree(form, B, T, H):
     """With the test hook that makes every tensor map fail, the backward kernels load their inputs with plain loads
     (and the forward falls back to its one-group form): the gradients are bit-identical to those of the TMA paths,
