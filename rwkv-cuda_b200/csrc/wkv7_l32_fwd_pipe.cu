@@ -10,7 +10,8 @@
 //   chain group, chunk c:     the dependent chain X, Z, SA, Y and the state update, y out, decay scaling.
 // Three sets of operand arrays and two sets of token x token matrices are handed on through mbarriers
 // (full / empty; an operand set is released by the matrix group and by the chain group); inside a group the
-// warps synchronise on a named barrier.  One thread block per SM (220 KB of shared memory, 256 columns of
+// warps synchronise on a named barrier.  A thirteenth warp issues the bulk copies (a lane of the loader group pays
+// about 55 cycles per copy; with the warp of its own B = 16, T = 4096 goes from 1.715 to 1.697 ms).  One thread block per SM (220 KB of shared memory, 256 columns of
 // tensor memory).  Measured per chunk: loader 3.7 k cycles, matrix group 3.1 k, chain group 3.4 k, against
 // 7.2 k for one thread block of wkv7_l32_fwd.cu alone and 11 k with three on an SM (3.7 k per chunk and SM):
 // B = 16, T = 4096 1.70 ms against 1.94 ms, B = 2 0.27 ms against 0.48 ms.  What did not help: the 192 rows of
@@ -44,7 +45,7 @@ namespace v7q {
 using namespace v7x;
 
 constexpr int GNT = 128;          // threads per group
-constexpr int PNT = 3 * GNT;
+constexpr int PNT = 3 * GNT + 32;   // three groups and the warp that issues the bulk copies
 constexpr int NA = 3;             // operand sets in flight
 constexpr int NU = 2;             // matrix sets in flight
 constexpr int NS = 2;             // chunks of raw input rows in flight (bulk copies)
@@ -87,9 +88,10 @@ __device__ __forceinline__ void mbar_init_count(uint64_t* bar, int count) {
 }
 
 // mbarriers: operand set full (loader -> matrix group) / empty (two arrivals: matrix and chain group);
-// matrix set full (matrix -> chain group; it implies the operand set) / empty; U done; Y, S done; the chain's own
+// matrix set full (matrix -> chain group; it implies the operand set) / empty; U done; Y, S done; the chain's own;
+// the raw rows of a stage have landed / have been taken into registers by the loader group (loader -> issuing warp)
 enum { kFullA = 0, kEmptyA = kFullA + NA, kFullU = kEmptyA + NA, kEmptyU = kFullU + NU, kFU = kEmptyU + NU, kBY, kBS, kBChain,
-       kRawFull, kNBar = kRawFull + NS };
+       kRawFull, kTaken = kRawFull + NS, kNBar = kTaken + NS };
 
 __global__ void __launch_bounds__(PNT, 1)
 wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_constant__ InputMaps maps, bf16* __restrict__ y_,
@@ -144,23 +146,10 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_c
         // ================================ loader group =====================================================
         float* Hs = reinterpret_cast<float*>(smem + PipeSmem::kHs);
         // The raw rows of a chunk (6 tensors x 32 tokens x 128 bytes) come in as six tiled bulk copies (TMA), issued
-        // by one thread two chunks ahead and counted on an mbarrier; every thread then takes its part (a channel
+        // by the thirteenth warp two chunks ahead and counted on an mbarrier; every thread then takes its part (a channel
         // pair of 8 tokens per tensor) into registers.  Rows beyond the sequence belong to the next batch row or
         // lie outside the tensor (read as zeros); they are masked when the registers are filled.
         unsigned char* stg = smem + PipeSmem::kRaw;
-        int issued = 0;
-        // (every warp's lane 0 issues its share of the six tiles: an issue costs the thread about 55 cycles)
-        auto issue_raw = [&](int c) {
-            const int st = c & 1;
-            uint64_t* fb = bar + kRawFull + st;
-            if (lane == 0) {
-                if (wg == 0) mbar_expect_tx(fb, 6 * 32 * 128);
-                for (int x = wg; x < 6; x += 4) tma_tile(stg + (st * 6 + x) * 32 * 128, &maps.m[x], hh * 64, bb * T + c * LC, fb);
-            }
-            issued = c + 1;
-        };
-        issue_raw(0);
-        if (nchunks > 1) issue_raw(1);
         int sa = 0, ua = 0;   // operand set of this chunk, how often it has been used before
         int c = 0;
         for (; c < nchunks; ++c) {
@@ -182,9 +171,9 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_c
             PIPE_MARK(3);
             if (fail) atomicMax(const_cast<int*>(abort_word), fail);
             if (gtid == 0) gabort[0] = *abort_word;
-            group_sync(gbar, GNT);   // (every thread has taken its part of the rows: the stage may be refilled)
+            group_sync(gbar, GNT);
+            if (gtid == 0) mbar_arrive(bar + kTaken + st);   // every thread has taken its part of the rows: the stage may be refilled
             if (gabort[0]) break;
-            if (c + NS < nchunks) issue_raw(c + NS);
             PIPE_MARK(4);
             prepare_operands<6, 8, 4>(raw, valid, A, A + ARR64, A + 2 * ARR64, HALF32, nullptr, 0, We, Hs, nullptr, wg, lane, gbar);
             proxy_fence();
@@ -194,8 +183,6 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_c
             if (++sa == NA) { sa = 0; ++ua; }
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
-        // leaving early: the copies that are still in flight must have landed before the block may end
-        for (int cc = c; cc < issued; ++cc) mbar_wait(bar + kRawFull + (cc & 1), (cc >> 1) & 1);
     } else if (grp == 1) {
         // ================================ matrix group =====================================================
         float* Uab = reinterpret_cast<float*>(smem + PipeSmem::kUab);
@@ -241,6 +228,27 @@ wkv7q_forward_kernel(int T, int H, const float* __restrict__ s0_, const __grid_c
             if (++sa == NA) { sa = 0; ++ua; }
         }
         if (fail) atomicMax(const_cast<int*>(abort_word), fail);
+    } else if (grp == 3) {
+        // ================================ the warp that issues the bulk copies ==============================
+        // One lane asks for the six tiles of a chunk, NS chunks ahead, as soon as the loader group has taken the
+        // chunk that held the stage before (an issue costs a thread about 55 cycles: too much for the loader's lanes).
+        if (lane == 0) {
+            unsigned char* stg = smem + PipeSmem::kRaw;
+            int c = 0;
+            for (; c < nchunks; ++c) {
+                const int st = c & 1;
+                if (c >= NS && !mbar_wait(bar + kTaken + st, ((c >> 1) - 1) & 1)) { fail = 32; break; }
+                if (*abort_word) break;
+                uint64_t* fb = bar + kRawFull + st;
+                mbar_expect_tx(fb, 6 * 32 * 128);
+#pragma unroll
+                for (int x = 0; x < 6; ++x) tma_tile(stg + (st * 6 + x) * 32 * 128, &maps.m[x], hh * 64, bb * T + c * LC, fb);
+            }
+            if (fail) atomicMax(const_cast<int*>(abort_word), fail);
+            // leaving early: the copies that are still in flight must have landed before the block may end
+            if (*abort_word)
+                for (int cc = max(0, c - NS); cc < c; ++cc) mbar_wait(bar + kRawFull + (cc & 1), (cc >> 1) & 1);
+        }
     } else {
         // ================================ chain group ======================================================
         {   // initial state -> tensor memory (and saved as the start state of chunk 0)
