@@ -155,6 +155,18 @@ __device__ __forceinline__ void group_sync(int id, int nthreads) {
     else asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// A [32 tokens][64 channels] bf16 tile (4 KB) for an output whose elements come out of tensor memory one
+// (token, channel) at a time: written as two-byte words, read back as 16-byte pieces that go to global memory as
+// whole pieces of a row.  The pieces of a row are XOR-ed with the token so that neither side has bank conflicts.
+__device__ __forceinline__ int stage_off(int tt, int ch) { return tt * 128 + ((((ch >> 3) ^ tt) & 7) << 4) + (ch & 7) * 2; }
+// thread idx (0..255) = (token, piece): the piece of the staged tile -> out[(token0 + token) * C + 8 * piece ..]
+__device__ __forceinline__ void stage_flush(const unsigned char* stage, bf16* out, i64 row0_off, int C, int idx, int valid) {
+    const int tt = idx >> 3, piece = idx & 7;
+    if (tt < valid)
+        *reinterpret_cast<uint4*>(out + row0_off + (i64)tt * C + piece * 8) =
+            *reinterpret_cast<const uint4*>(stage + tt * 128 + ((piece ^ (tt & 7)) << 4));
+}
+
 // ---- the part of a chunk that does not depend on the carried state ---------------------------------
 // Raw inputs of one chunk as loaded by a thread: channels (2*lane, 2*lane+1) of TPW consecutive tokens
 // (token index inside the chunk = TPW*warp + q).  NX tensors: r w k v a b [dy].

@@ -209,11 +209,13 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             __syncthreads();   // the tiles lie where the state and the scratch of the preparation go next
         }
         fetch_state(c);
-        // the zero blocks of D0 (its space was used by P)
+        // the zero blocks of D0 (its space was used by P), and N1 (it held the staged dv; only its upper right block is
+        // written below, the rest has to read as zero)
         {
             const int s = tid >> 4, cc = tid & 15;   // 16 x 16
             *reinterpret_cast<float*>(D0 + sw32(s, 16 + cc)) = 0.f;
             *reinterpret_cast<float*>(D0 + sw32(16 + s, cc)) = 0.f;
+            reinterpret_cast<float4*>(N1)[tid] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         // ---- 1. operands ---------------------------------------------------------------------------
         prepare_operands<7, BTPW, 8>(raw, valid, AR, BK, SV + 32 * 128, HALF64, EY + 32 * 128, HALF64, We, Hs, Lam, warp, lane);
@@ -336,7 +338,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 for (int e = 0; e < 4; ++e) {
                     const int i = row0 + g + ((e & 2) ? 8 : 0), tt = 16 * hs + nt * 8 + 2 * t + (e & 1);
                     *reinterpret_cast<float*>(EY + sw(tt, i, HALF64)) = tf32rf(ev[nt][e]);
-                    if (tt < valid) dv_[tok0 + (i64)(c * LC + tt) * C + i] = __float2bfloat16_rn(dv[nt][e]);
+                    *reinterpret_cast<bf16*>(N1 + stage_off(tt, i)) = __float2bfloat16_rn(dv[nt][e]);   // N1 is dead: staged, sent with the others
                 }
         }
         proxy_fence();
@@ -504,6 +506,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 *reinterpret_cast<uint4*>(db_ + o) = *reinterpret_cast<const uint4*>(stg[3] + tt * 72 + piece * 8);
             }
         }
+        stage_flush(N1, dv_, tok0 + (i64)c * LC * C, C, tid, valid);
         __syncthreads();
         {
             const int tt = tid >> 3, piece = tid & 7;
