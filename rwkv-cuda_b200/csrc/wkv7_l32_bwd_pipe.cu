@@ -213,6 +213,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 *reinterpret_cast<uint4*>(db_ + o) = *reinterpret_cast<const uint4*>(st3);
                 *reinterpret_cast<uint4*>(dw_ + o) = *reinterpret_cast<const uint4*>(st3 + 32 * 72);
             }
+            stage_flush(sbase_ + SetSmem::kN1, dv_, tok0 + (i64)cp * LC * C, C, gtid, min(LC, T - cp * LC));
         };
         uint32_t par = 0;
         int it = 0;
@@ -258,10 +259,12 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                 }
                 cp_async_commit();
             }
-            {   // the zero blocks of D0 (its space was used by P)
+            {   // the zero blocks of D0 (its space was used by P), and N1 (it held the staged dv; only its upper right
+                // block is written below, the rest has to read as zero)
                 const int s = gtid >> 4, cc = gtid & 15;
                 *reinterpret_cast<float*>(D0 + sw32(s, 16 + cc)) = 0.f;
                 *reinterpret_cast<float*>(D0 + sw32(16 + s, cc)) = 0.f;
+                reinterpret_cast<float4*>(N1)[gtid] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
             prepare_operands<7, 4, 8>(raw, valid, AR, BK, SV + 32 * 128, HALF64, EY + 32 * 128, HALF64, We, Hs, Lam, wg, lane, gbar);
             cp_async_wait<0>();
@@ -350,6 +353,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             unsigned char* base = smem + set * PipeSmem::kSet1;
             unsigned char *AR = base + SetSmem::kAR, *BK = base + SetSmem::kBK, *SV = base + SetSmem::kSV, *EY = base + SetSmem::kEY;
             unsigned char *S0 = base + SetSmem::kS0, *Pm = base + SetSmem::kP;
+            unsigned char* N1b = base + SetSmem::kN1;
             const float* Lam = reinterpret_cast<const float*>(base + SetSmem::kLam);
             const float* We = reinterpret_cast<const float*>(base + SetSmem::kWe);
             const uint32_t arA = smem_u32(AR), bkA = smem_u32(BK), svA = smem_u32(SV), eyA = smem_u32(EY), s0A = smem_u32(S0);
@@ -442,7 +446,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
                     for (int e = 0; e < 4; ++e) {
                         const int i = row0 + g + ((e & 2) ? 8 : 0), tt = 16 * hs + nt * 8 + 2 * t + (e & 1);
                         *reinterpret_cast<float*>(EY + sw(tt, i, HALF64)) = tf32rf(ev[nt][e]);
-                        if (tt < valid) dv_[tok0 + (i64)(c * LC + tt) * C + i] = __float2bfloat16_rn(dv[nt][e]);
+                        *reinterpret_cast<bf16*>(N1b + stage_off(tt, i)) = __float2bfloat16_rn(dv[nt][e]);   // N1 is dead: staged, sent with the others
                     }
             }
             proxy_fence();
