@@ -169,11 +169,12 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     // The same through the copy engine, when tensor maps could be made: one thread asks for the tiles of chunk c
     // (counted in bytes on mbarrier 6), and at the top of that chunk every thread takes its words out of the staged tiles.
     constexpr int kRawBytes = 4 * 4096 + (WMODE == 1 ? 4096 : WMODE == 0 ? 8192 : 0);
+    // (called by every thread: lane 0 of warp x asks for tile x, an issue costs a thread about 55 cycles; warp 0
+    // announces the bytes, which may happen before or after the other warps' copies complete)
     auto request = [&](int c) {
-        mbar_expect_bytes(bar + 6, kRawBytes);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) tma_tile_load(Raw + x * 4096, &maps.m[x], hh * 64, bb * T + c * LC, bar + 6);
-        if (WMODE <= 1) tma_tile_load(Raw + 4 * 4096, &maps.m[4], hh * 64, bb * T + c * LC, bar + 6);
+        if (lane != 0) return;
+        if (warp == 0) mbar_expect_bytes(bar + 6, kRawBytes);
+        if (warp < 4 || (warp == 4 && WMODE <= 1)) tma_tile_load(Raw + warp * 4096, &maps.m[warp], hh * 64, bb * T + c * LC, bar + 6);
     };
     auto take = [&](int c) {
         const int t0 = c * LC + BTPW * warp;
@@ -205,7 +206,7 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
     };
     if (!staged) fetch(nchunks - 1);
-    else { if (tid == 0) request(nchunks - 1); pending = true; }
+    else { request(nchunks - 1); pending = true; }
     // two chunks ahead, into L2: the chunk-start state (the input tiles come by the copy engine one chunk ahead)
     auto ask_l2 = [&](int c) {
         if (tid != 224) return;
@@ -247,7 +248,7 @@ wkv6b_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             }
             *reinterpret_cast<float2*>(Hs + warp * 64 + j0) = make_float2(run0, run1);
             __syncthreads();
-            if (staged && c > 0) { if (tid == 0) request(c - 1); pending = true; }   // every thread has taken its words: the stage is free
+            if (staged && c > 0) { request(c - 1); pending = true; }   // every thread has taken its words: the stage is free
             float base0 = 0.f, base1 = 0.f, tot0 = 0.f, tot1 = 0.f;
 #pragma unroll
             for (int gq = 0; gq < 8; ++gq) {

@@ -175,10 +175,21 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     // its words out of them; without maps every thread loads its words itself, one chunk ahead, into registers.
     const bool staged = maps.valid != 0;
     bool pending = false;   // a request whose tiles have not been taken yet
+    // (called by every thread: lane 0 of warp x asks for tile x, an issue costs a thread about 55 cycles; warp 0
+    // announces the bytes, which may happen before or after the other warps' copies complete)
     auto request = [&](int c) {
-        mbar_expect_bytes(bar + 7, 7 * 4096);
-#pragma unroll
-        for (int x = 0; x < 7; ++x) tma_tile_load(Raw + x * 4096, &maps.m[x], hh * 64, bb * T + c * LC, bar + 7);
+        if (lane != 0) return;
+        if (warp == 0) mbar_expect_bytes(bar + 7, 7 * 4096);
+        if (warp < 7) tma_tile_load(Raw + warp * 4096, &maps.m[warp], hh * 64, bb * T + c * LC, bar + 7);
+    };
+    // the chunk after next into L2: lane 1 of warp x asks for tile x, warp 7 for the chunk-start state
+    auto ask_l2 = [&](int c) {
+        if (lane != 1 || !maps.valid) return;
+        if (warp < 7) l2_prefetch_tile(&maps.m[warp], hh * 64, bb * T + c * LC);
+        else {
+            const float* sp = ck + (i64)c * 64 * 64;
+            if ((reinterpret_cast<uintptr_t>(sp) & 15) == 0) l2_prefetch(sp, 64 * 64 * 4);
+        }
     };
     auto take = [&](int c) {
         const int t0 = c * LC + BTPW * warp;
@@ -188,9 +199,9 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             for (int q = 0; q < BTPW; ++q)
                 raw.x[x][q] = (t0 + q < T) ? *reinterpret_cast<const uint32_t*>(Raw + x * 4096 + (BTPW * warp + q) * 128 + lane * 4) : 0u;
     };
-    if (staged) { if (tid == 0) request(nchunks - 1); pending = true; }
+    if (staged) { request(nchunks - 1); pending = true; }
     else fetch_chunk<7, BTPW>(raw, src, tok0, C, nchunks - 1, T, warp, lane);
-    if (nchunks > 1 && tid == 224) prefetch_chunk_l2<7>(maps, hh * 64, bb * T + (nchunks - 2) * LC, ck + (i64)(nchunks - 2) * 64 * 64, 64 * 64 * 4);
+    if (nchunks > 1) ask_l2(nchunks - 2);
     int fail = 0;
     uint32_t par = 0;
     ChainSync cs{bar + 6, 0, 0};   // used by warp 0 only
@@ -279,7 +290,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             tmem_wait_st();
         }
         if (c > 0 && !staged) fetch_chunk<7, BTPW>(raw, src, tok0, C, c - 1, T, warp, lane);   // under the chain
-        if (c > 1 && tid == 224) prefetch_chunk_l2<7>(maps, hh * 64, bb * T + (c - 2) * LC, ck + (i64)(c - 2) * 64 * 64, 64 * 64 * 4);   // the one after into L2
+        if (c > 1) ask_l2(c - 2);
         WKV7_PHASE(5);   // issue of the forward part, decay scaling of E, request of the next chunk
         if (!mbar_wait(bar + 1, par)) fail = 2;
         tc_fence_after();
@@ -482,7 +493,7 @@ wkv7x_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
         }
         __syncthreads();
         // every product that reads EY or S0 has completed and every thread has taken its anchor from S0
-        if (staged && c > 0) { if (tid == 0) request(c - 1); pending = true; }
+        if (staged && c > 0) { request(c - 1); pending = true; }
         WKV7_PHASE(13);  // epilogue part 1
 #pragma unroll
         for (int h = 0; h < 2; ++h) {

@@ -182,19 +182,23 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
     // thread of the back group after its last products (by the front group for the first two chunks), counted in
     // bytes on the set's mbarrier; the front group takes its words out of the tiles before it writes the set.
     const bool staged = maps.valid != 0;
+    // (called by every thread of a group: lane 0 of the group's warp x asks for tile x, an issue costs a thread about
+    // 55 cycles; warp 0 announces the bytes, which may happen before or after the other warps' copies complete)
     auto request = [&](int set, int c) {
+        if (lane != 0) return;
         unsigned char* dst = smem + set * PipeSmem::kSet1 + SetSmem::kEY;
-        mbar_expect_bytes(bar + kRaw + set, 7 * 4096);
-#pragma unroll
-        for (int x = 0; x < 7; ++x) tma_tile_load(dst + x * 4096, &maps.m[x], hh * 64, bb * T + c * LC, bar + kRaw + set);
-        raw_req[set] = raw_req[set] + 1;
+        if (wg == 0) {
+            mbar_expect_bytes(bar + kRaw + set, 7 * 4096);
+            raw_req[set] = raw_req[set] + 1;
+        }
+        if (wg < 7) tma_tile_load(dst + wg * 4096, &maps.m[wg], hh * 64, bb * T + c * LC, bar + kRaw + set);
     };
 
     // ================================ front group ==========================================================
     if (grp == 0) {
         RawChunk<7, 4> raw;
         if (!staged) fetch_chunk<7, 4>(raw, src, tok0, C, nchunks - 1, T, wg, lane);
-        else if (gtid == 0) {
+        else {
             request(0, nchunks - 1);
             if (nchunks > 1) request(1, nchunks - 2);
         }
@@ -586,7 +590,7 @@ wkv7p_backward_kernel(int T, int H, const bf16* __restrict__ r_, const bf16* __r
             group_sync(gbar, GNT);
             // every product that reads EY or S0 of this set has completed and every thread has taken its anchor from S0:
             // the tiles of the chunk that uses the set next may come
-            if (staged && c >= 2 && gtid == 0) request(set, c - 2);
+            if (staged && c >= 2) request(set, c - 2);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int j = row0 + g + 8 * h;
